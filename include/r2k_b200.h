@@ -1,0 +1,239 @@
+/*
+ * r2k_b200 -- C ABI of the B200 (sm_100a) SSPA packed-KV decode path.
+ *
+ * Plain pointers and sizes only; no torch types.  Every entry point returns an
+ * int status (R2K_OK == 0), never throws, never synchronises the device and
+ * never allocates device memory (workspaces are caller-provided).  All device
+ * work is enqueued on the stream passed as `stream` (a cudaStream_t cast to
+ * void*; NULL is the legacy default stream).
+ *
+ * Each declaration names the routine of the reference implementation
+ * (Fabulous1496/R2-Omni, paths relative to that project) that it replaces.
+ */
+#ifndef R2K_B200_H
+#define R2K_B200_H
+
+#include <stddef.h>
+#include <stdint.h>
+
+#ifdef __cplusplus
+extern "C" {
+#endif
+
+/* ---- status codes ------------------------------------------------------ */
+enum {
+  R2K_OK = 0,
+  R2K_ERR_NULL = 1,          /* a required pointer is NULL                           */
+  R2K_ERR_GEOMETRY = 2,      /* unsupported or inconsistent shapes                   */
+  R2K_ERR_ALIGNMENT = 3,     /* a base pointer or stride is not 16-byte aligned      */
+  R2K_ERR_CAPACITY = 4,      /* an arena or the residual ring has no room            */
+  R2K_ERR_WORKSPACE = 5,     /* workspace too small                                  */
+  R2K_ERR_CUDA = 6,          /* a CUDA runtime call failed (launch, attribute, ...)  */
+  R2K_ERR_DEVICE_TIMEOUT = 7,/* a bounded device-side wait gave up (see r2k_decode_device_status) */
+  R2K_ERR_EMPTY = 8          /* the cache holds no token to attend to                */
+};
+
+/* element type of queries, bf16-value pages, the residual window and the output */
+enum { R2K_DTYPE_BF16 = 0, R2K_DTYPE_FP16 = 1 };
+
+/* r2k_decode flags */
+enum {
+  R2K_FLAG_OUTPUT_HADAMARD = 1, /* round to the element type, then 128-point orthonormal WHT
+                                   (r2omni/sspa/kernels/triton_fourq_splitk.py:999-1005)   */
+  R2K_FLAG_OUT_F32 = 2,         /* `out` is float32 [B,Hq,128] instead of the element type  */
+  R2K_FLAG_OUT_STATE = 4        /* `out` is float32 [B,Hq,130]: (max, sum-exp, un-normalised
+                                   weighted V[128]) in natural-log units, for cross-shard merge */
+};
+
+/*
+ * Geometry of one homogeneous batch of caches (every request has the same
+ * extents; only the residual-window length differs per request).  Mirrors the
+ * scalar fields r2omni/sspa/kernels/triton_fourq_splitk.py:1833-1907
+ * (prepare_splitk_executor) extracts from a ThreePrecisionCache.
+ */
+typedef struct R2KGeom {
+  int32_t batch;            /* B                                                        */
+  int32_t num_q_heads;      /* Hq                                                       */
+  int32_t num_kv_heads;     /* Hkv; Hq % Hkv == 0 and Hq / Hkv <= 8                     */
+  int32_t head_dim;         /* must be 128                                              */
+  int32_t dtype;            /* R2K_DTYPE_*                                              */
+  int32_t page_size;        /* 16, 32 or 64 (residual page-length bookkeeping)          */
+  int32_t k_block;          /* tokens per key calibration block: 32, 64 or 128          */
+  int32_t v2_group;         /* INT2-value group width along head_dim: 32, 64 or 128     */
+  int32_t n_fp;             /* tokens in the bf16-value pool                            */
+  int32_t n_i4;             /* tokens in the INT4-value pool                            */
+  int32_t n_i2;             /* tokens in the INT2-value pool (static + flushed)         */
+  int32_t k_capacity;       /* token rows per head of the key arena (multiple of 128)   */
+  int32_t k_off_fp;         /* key-arena row of the first token of each pool            */
+  int32_t k_off_i4;
+  int32_t k_off_i2;
+  int32_t fp_capacity;      /* token rows per head of the bf16-value array              */
+  int32_t i4_capacity;      /* token rows per head of the INT4-value arrays             */
+  int32_t i2_capacity;      /* token rows per head of the INT2-value arena              */
+  int32_t recent_capacity;  /* token rows per head of the residual ring                 */
+  float sm_scale;           /* softmax scale; <= 0 selects head_dim^-0.5                */
+} R2KGeom;
+
+/*
+ * Device pointers of one batch of caches.  Each pointer addresses request 0;
+ * request b lives `*_bstride` BYTES further (0 is fine for B == 1).  Layouts
+ * are the reference's storage formats, bit for bit:
+ *   k_packed  u8  [Hkv, k_capacity, 64]   byte j = code(2j) | code(2j+1) << 4
+ *   k_scale   f16 [Hkv, k_capacity/k_block, 128], k_zero u8 same shape
+ *             (r2omni/sspa/runtime/compact_int4_key.py:95-109, 241-249)
+ *   fp_v      T   [Hkv, fp_capacity, 128]
+ *   i4_packed u8  [Hkv, i4_capacity, 64]  two's-complement nibbles, even dim low
+ *   i4_scale  f32 [Hkv, i4_capacity]      (r2omni/sspa/runtime/fused_value_pack.py:52-70)
+ *   i2_packed u8  [Hkv, i2_capacity, 32]  byte j = c(4j)|c(4j+1)<<2|c(4j+2)<<4|c(4j+3)<<6
+ *   i2_scale  f16 [Hkv, i2_capacity, 128/v2_group], i2_zero u8 same shape
+ *             (r2omni/sspa/runtime/fused_value_pack.py:107-149)
+ *   recent_k/v T  [Hkv, recent_capacity, 128], recent_len i32 [1] per request,
+ *   recent_global / recent_logical i64 [recent_capacity],
+ *   recent_page_lengths i64 [recent_capacity / page_size]
+ *             (r2omni/sspa/runtime/precision_pool.py:747-784)
+ * Pointers of an empty pool may be NULL.
+ */
+typedef struct R2KCacheView {
+  const uint8_t* k_packed;  const void* k_scale;  const uint8_t* k_zero;
+  const void* fp_v;
+  const uint8_t* i4_packed; const float* i4_scale;
+  const uint8_t* i2_packed; const void* i2_scale; const uint8_t* i2_zero;
+  void* recent_k; void* recent_v; int32_t* recent_len;
+  int64_t* recent_global; int64_t* recent_logical; int64_t* recent_page_lengths;
+  int64_t k_packed_bstride, k_scale_bstride, k_zero_bstride;
+  int64_t fp_v_bstride;
+  int64_t i4_packed_bstride, i4_scale_bstride;
+  int64_t i2_packed_bstride, i2_scale_bstride, i2_zero_bstride;
+  int64_t recent_k_bstride, recent_v_bstride, recent_len_bstride;
+  int64_t recent_global_bstride, recent_logical_bstride, recent_page_lengths_bstride;
+} R2KCacheView;
+
+/* One token appended in the same launch as the decode it takes part in. */
+typedef struct R2KAppend {
+  const void* k;              /* T [B, Hkv, 128]; NULL = no append                      */
+  const void* v;              /* T [B, Hkv, 128]                                        */
+  const int64_t* indices;     /* optional device i64 [B,2] (global index, logical position)
+                                 per request; NULL = use the two scalars for every request */
+  int64_t global_index;
+  int64_t logical_position;
+} R2KAppend;
+
+/* ---- decode ------------------------------------------------------------ */
+
+/* Bytes of scratch r2k_decode needs for this geometry on the current device.
+ * Replaces allocate_splitk_workspace / required_splitk_blocks
+ * (r2omni/sspa/kernels/triton_fourq_splitk.py:1607-1692). */
+int r2k_decode_workspace_bytes(const R2KGeom* geom, size_t* bytes);
+
+/* Clears the arrival counters at the head of a workspace.  Call once after
+ * allocating it (and after any decode that reported a device timeout).        */
+int r2k_decode_workspace_init(void* workspace, size_t bytes, void* stream);
+
+/*
+ * One decode step over a batch of packed caches: split-K partial attention over
+ * the INT4 keys and bf16/INT4/INT2 value pools plus the residual window, exact
+ * (max, sum-exp, out) merge, optional Hadamard epilogue and optional fused
+ * one-token append into the residual ring -- a single launch.
+ *   q   : T [B, Hq, 128] contiguous;  out: see R2K_FLAG_OUT_*.
+ * With `append`, the new token takes part in the attention and is then written
+ * to ring row recent_len[b]; recent_len, the two index arrays and the page
+ * length are updated on the device.  The ring must have room (host-checked by
+ * the caller, as in the reference).
+ * Replaces SplitKExecutor.__call__ and its three launches
+ * (r2omni/sspa/kernels/triton_fourq_splitk.py:1243-1547: _fourq_page_partial_kernel
+ * :449-931, _fourq_hierarchical_group_reduce_kernel :1023-1086,
+ * _fourq_partial_reduce_kernel :936-1020).
+ */
+int r2k_decode(const R2KGeom* geom, const R2KCacheView* view, const void* q, const R2KAppend* append,
+               void* workspace, size_t workspace_bytes, void* out, uint32_t flags, void* stream);
+
+/* Copies the device-side status word of the last decodes that used `workspace`
+ * into *status (R2K_OK or R2K_ERR_DEVICE_TIMEOUT).  Synchronises `stream`.     */
+int r2k_decode_device_status(void* workspace, int32_t* status, void* stream);
+
+/* Number of kernels of this library launched by this process so far. */
+uint64_t r2k_launch_count(void);
+
+/*
+ * Merge `num_states` un-normalised attention states (each float32 [rows,130] as
+ * written by R2K_FLAG_OUT_STATE, `state_stride` floats apart) into the final
+ * output [rows,128] (element type, or float32 with R2K_FLAG_OUT_F32; Hadamard
+ * flag honoured).  rows = B*Hq.  This is the cross-GPU step of the
+ * sequence-sharded path; the arithmetic is _merge_state of
+ * r2omni/sspa/kernels/triton_fourq_attention.py:58-69.
+ */
+int r2k_merge_states(const float* states, int32_t num_states, int64_t state_stride, int32_t rows,
+                     int32_t dtype, void* out, uint32_t flags, void* stream);
+
+/* ---- quantize and pack -------------------------------------------------- */
+
+/*
+ * Per-channel affine INT4 key blocks.  Gathers `count` rows src[h, index[i], :]
+ * (index == NULL: rows 0..count-1) of a T [Hkv, src_rows, 128] tensor into arena
+ * rows dst_start .. dst_start+count-1 and calibrates every k_block-token block
+ * those rows touch.  When dst_start is not a multiple of k_block, the rows
+ * already stored in front of it inside that block are dequantised, rounded to T
+ * and re-quantised together with the new rows, exactly as
+ * CompactInt4KeyArena.append_superblock does.
+ * Replaces quantize_int4_key_per_channel / _gather_pack_int4_key_kernel /
+ * CompactInt4KeyArena._write / append_superblock
+ * (r2omni/sspa/runtime/compact_int4_key.py:21-110, 200-220).
+ */
+int r2k_pack_k_int4(const void* src, int32_t dtype, int32_t num_kv_heads, int64_t src_rows,
+                    const int64_t* index, int64_t count,
+                    uint8_t* k_packed, void* k_scale, uint8_t* k_zero,
+                    int64_t k_capacity, int32_t k_block, int64_t dst_start, void* stream);
+
+/* Per-token symmetric INT4 values (scale = max(amax/7, 1e-6), codes -7..7).
+ * Replaces _gather_pack_int4_value_kernel and make_packed_tensor(.,4,"per_token",2)
+ * (r2omni/sspa/runtime/fused_value_pack.py:25-70, r2omni/sspa/runtime/quantization.py:19-50, 77-102). */
+int r2k_pack_v_int4(const void* src, int32_t dtype, int32_t num_kv_heads, int64_t src_rows,
+                    const int64_t* index, int64_t count,
+                    uint8_t* packed, float* scale, int64_t capacity, int64_t dst_start, void* stream);
+
+/* Per-token, per-group affine INT2 values (range widened to contain 0).
+ * Replaces _gather_pack_int2_value_kernel and quantize_int2_value
+ * (r2omni/sspa/runtime/fused_value_pack.py:72-149, r2omni/sspa/runtime/int2_reference.py:96-151). */
+int r2k_pack_v_int2(const void* src, int32_t dtype, int32_t num_kv_heads, int64_t src_rows,
+                    const int64_t* index, int64_t count,
+                    uint8_t* packed, void* scale, uint8_t* zero, int64_t capacity, int32_t group,
+                    int64_t dst_start, void* stream);
+
+/* Row gather dst[h, dst_start+i, :] = src[h, index[i], :] for 128-wide T rows
+ * (the bf16-value pool of build_three_precision_cache,
+ * r2omni/sspa/runtime/precision_pool.py:708, 733-735). */
+int r2k_gather_rows(const void* src, int32_t num_kv_heads, int64_t src_rows, const int64_t* index,
+                    int64_t count, void* dst, int64_t dst_rows, int64_t dst_start, void* stream);
+
+/* ---- residual window ---------------------------------------------------- */
+
+/*
+ * Standalone one-token append into the residual ring of every request of the
+ * batch (row recent_len[b]; updates recent_len, index arrays, page length).
+ * Replaces append_recent_fp_triton / _append_recent_fp_kernel
+ * (r2omni/sspa/kernels/triton_fourq_splitk.py:413-447, 1557-1604).
+ */
+int r2k_append_recent(const R2KGeom* geom, const R2KCacheView* view, const R2KAppend* append, void* stream);
+
+/*
+ * Flush: quantize-and-pack the oldest `flush_tokens` rows of the residual ring
+ * of every request into key-arena rows k_dst.. (with tail re-quantisation) and
+ * INT2-value rows v_dst.., copy their global/logical indices to
+ * i2_global/i2_logical (i64 arrays, row v_meta_dst.., may be NULL), slide the
+ * remaining `ring_tokens - flush_tokens` rows to the front and set recent_len
+ * and the page lengths accordingly.  `ring_tokens` is the host mirror of the
+ * ring length.  All on `stream`, no host synchronisation.
+ * Replaces the flush branch of append_generated_token
+ * (r2omni/sspa/runtime/dynamic_fourq_cache.py:195-254).
+ */
+int r2k_flush_recent(const R2KGeom* geom, const R2KCacheView* view, int32_t ring_tokens, int32_t flush_tokens,
+                     int64_t k_dst, int64_t v_dst,
+                     int64_t* i2_global, int64_t* i2_logical, int64_t meta_bstride, int64_t v_meta_dst,
+                     void* stream);
+
+const char* r2k_status_string(int status);
+
+#ifdef __cplusplus
+}
+#endif
+#endif /* R2K_B200_H */

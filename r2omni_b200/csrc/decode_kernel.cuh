@@ -1,0 +1,777 @@
+// Packed-KV GQA decode for sm_100a: one launch per decode step.
+//
+// Replaces the reference's three launches (tile partials, 64-way group
+// reduce, final reduce + Hadamard + fused append;
+// r2omni/sspa/kernels/triton_fourq_splitk.py:449-1020, 1243-1547).
+//
+// Shape of the kernel
+//   * grid = 2 CTAs per SM; every CTA owns a contiguous, byte-balanced range of
+//     the flat tile list (request, kv head, pool, tile) and keeps ONE running
+//     (max, sum-exp, out) state per (request, kv head) it crosses.
+//   * warp 4 is the producer: it streams each tile's key nibbles, key
+//     scale/zero rows and value bytes into a 3-stage shared-memory ring with
+//     1-D bulk copies (TMA) completing on mbarriers.  Warps 0-3 consume.
+//   * tokens sit on the M axis of mma.sync.m16n8k16 and the (<= 8) query heads
+//     of the GQA group on N, so no MMA lane is padding:
+//       S^T[tok,head] = K[tok,ch] Q'^T[ch,head],  O^T[dim,head] += V^T[dim,tok] P^T[tok,head].
+//   * INT4 codes are fed to the tensor core as fp16 *subnormals* (code * 2^-24
+//     or code * 2^-20 straight out of an AND), so a key nibble costs 5/8 of an
+//     ALU instruction.  Per-channel key scales are folded into Q' once per
+//     32-token block as an exact two-term fp16 sum (hi + lo = q * scale), the zero points
+//     become one extra MMA chain per block, per-token INT4-value scales are
+//     folded into P, INT2 values are dequantised in registers.
+//   * partial states go to a small workspace; the last CTA to finish a
+//     (request, kv head) merges them, writes the output, applies the optional
+//     Hadamard epilogue and the fused append.
+//
+// Every wait is bounded: a wait that gives up records R2K_ERR_DEVICE_TIMEOUT in
+// the workspace, the warp stops consuming and the kernel still terminates.
+#pragma once
+
+#include "decode.cuh"
+#include "device_utils.cuh"
+
+namespace r2k {
+
+namespace {
+
+constexpr float kLn2 = 0.69314718055994531f;
+constexpr float k2p24 = 16777216.0f;
+constexpr float k2p20 = 1048576.0f;
+constexpr float k2m24 = 1.0f / 16777216.0f;
+constexpr float k2m20 = 1.0f / 1048576.0f;
+constexpr uint32_t kMaskLo = 0x000F000Fu;  // nibble 0 of each half-word -> code * 2^-24 as fp16
+constexpr uint32_t kMaskHi = 0x00F000F0u;  // nibble 1 of each half-word -> code * 2^-20 as fp16
+
+struct Tile {
+  int pool;   // 0 bf16-V, 1 INT4-V, 2 INT2-V, 3 residual
+  int win;    // first key-arena row of the window (pool 3: first ring row)
+  int lo, hi; // valid rows of the window, [lo, hi) relative to win
+};
+
+__device__ __forceinline__ Tile tile_of(const DecodeParams& p, int u) {
+  Tile t;
+  int a0, a1, len;
+  if (u < p.nF) {
+    t.pool = 0; t.win = p.wF0 + u * kTF; a0 = p.g.k_off_fp; a1 = a0 + p.g.n_fp; len = kTF;
+  } else if (u < p.nF + p.n4) {
+    t.pool = 1; t.win = p.w40 + (u - p.nF) * kTQ; a0 = p.g.k_off_i4; a1 = a0 + p.g.n_i4; len = kTQ;
+  } else if (u < p.nF + p.n4 + p.n2) {
+    t.pool = 2; t.win = p.w20 + (u - p.nF - p.n4) * kTQ; a0 = p.g.k_off_i2; a1 = a0 + p.g.n_i2; len = kTQ;
+  } else {
+    t.pool = 3; t.win = (u - p.nF - p.n4 - p.n2) * kTR; a0 = 0; a1 = p.g.recent_capacity; len = kTR;
+  }
+  t.lo = max(a0 - t.win, 0);
+  t.hi = min(a1 - t.win, len);
+  return t;
+}
+
+// The unit range [u0,u1) of (request,kv head) `bh` owned by CTA `cta`.
+__device__ __forceinline__ void unit_range(const DecodeParams& p, int cta, int bh, int& u0, int& u1) {
+  const int64_t base = (int64_t)bh * p.c_bh;
+  int64_t lo = cta_cost_begin(p, cta) - base, hi = cta_cost_begin(p, cta + 1) - base;
+  lo = lo < 0 ? 0 : lo;
+  hi = hi > p.c_bh ? p.c_bh : hi;
+  u0 = units_before(p, lo);
+  u1 = units_before(p, hi);
+}
+
+template <bool BF16>
+__device__ __forceinline__ float elem_to_float(uint16_t raw) {
+  if (BF16) return __uint_as_float((uint32_t)raw << 16);
+  return __half2float(__ushort_as_half(raw));
+}
+
+// Row permutation inside a 16-token MMA tile: MMA row/k-slot r reads token
+// pi(r).  It keeps a thread's two key rows in one 128-byte line and makes the
+// four tokens of one value load alternate 64-byte halves (2-way instead of
+// 4-way shared-memory conflicts).
+__device__ __forceinline__ int pi_row(int r) {  // r in 0..7
+  return (r & ~1) + ((r & 1) ^ ((r >> 1) & 1));
+}
+
+struct WarpState {
+  float m[2];      // running max (log2 units) of heads 2t, 2t+1
+  float l[2];      // this lane's share of sum-exp
+  float lp[2];     // this lane's share of sum of fp16(p * scale) over INT4-value tokens (for the -8 code offset)
+  float o[8][4];   // O^T fragments: block j <-> dims 16g+2j (c0,c1) and 16g+2j+1 (c2,c3); columns = heads 2t,2t+1
+  int units;       // 0: true units; 1: INT4 units (even dims * 2^-24, odd dims * 2^-20)
+};
+
+__device__ __forceinline__ void state_reset(WarpState& s) {
+  s.m[0] = s.m[1] = -INFINITY;
+  s.l[0] = s.l[1] = s.lp[0] = s.lp[1] = 0.f;
+#pragma unroll
+  for (int j = 0; j < 8; ++j) s.o[j][0] = s.o[j][1] = s.o[j][2] = s.o[j][3] = 0.f;
+  s.units = 0;
+}
+
+__device__ __forceinline__ void set_units(WarpState& s, int units) {
+  if (s.units == units) return;
+  const float fe = units ? k2m24 : k2p24, fo = units ? k2m20 : k2p20;  // exact power-of-two rescale
+#pragma unroll
+  for (int j = 0; j < 8; ++j) { s.o[j][0] *= fe; s.o[j][1] *= fe; s.o[j][2] *= fo; s.o[j][3] *= fo; }
+  s.units = units;
+}
+
+// Online-softmax update for NT 16-token tiles of scores (log2 units, already
+// masked with -inf); returns probabilities in place.
+template <int NT>
+__device__ __forceinline__ void softmax_update(WarpState& st, float (&s)[NT][4]) {
+  float mx0 = -INFINITY, mx1 = -INFINITY;
+#pragma unroll
+  for (int j = 0; j < NT; ++j) {
+    mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][2]));
+    mx1 = fmaxf(mx1, fmaxf(s[j][1], s[j][3]));
+  }
+#pragma unroll
+  for (int d = 4; d < 32; d <<= 1) {
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, d));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, d));
+  }
+  const float n0 = fmaxf(st.m[0], mx0), n1 = fmaxf(st.m[1], mx1);
+  if (__any_sync(0xffffffffu, (n0 > st.m[0]) | (n1 > st.m[1]))) {
+    const float f0 = ex2_approx(st.m[0] - n0), f1 = ex2_approx(st.m[1] - n1);  // m = -inf -> 0
+    st.l[0] *= f0; st.l[1] *= f1; st.lp[0] *= f0; st.lp[1] *= f1;
+#pragma unroll
+    for (int j = 0; j < 8; ++j) { st.o[j][0] *= f0; st.o[j][1] *= f1; st.o[j][2] *= f0; st.o[j][3] *= f1; }
+    st.m[0] = n0; st.m[1] = n1;
+  }
+#pragma unroll
+  for (int j = 0; j < NT; ++j) {
+    s[j][0] = ex2_approx(s[j][0] - st.m[0]);
+    s[j][1] = ex2_approx(s[j][1] - st.m[1]);
+    s[j][2] = ex2_approx(s[j][2] - st.m[0]);
+    s[j][3] = ex2_approx(s[j][3] - st.m[1]);
+    st.l[0] += s[j][0] + s[j][2];
+    st.l[1] += s[j][1] + s[j][3];
+  }
+}
+
+// Scores of NT 16-token tiles against INT4 keys.  krows: shared-memory address
+// of the slice's first key row; ks/kz: the block's scale / zero rows.
+// Q' = q * scale is held as an exact two-term fp16 sum (hi = RN(q*s), lo = fma(q, s, -hi)),
+// so every product the tensor core sees is exact and the fp32 accumulation is the only rounding.
+template <int NT>
+__device__ __forceinline__ void qk_int4(const uint8_t* krows, const uint8_t* ks, const uint8_t* kz,
+                                        const uint32_t (&qh)[16], int t, int pg, float alpha, float (&s)[NT][4]) {
+  uint32_t qp[16], ql[16];  // paired (c0,c4) (c1,c5) (c2,c6) (c3,c7) per 8-channel word
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint4 w = *reinterpret_cast<const uint4*>(ks + 64 * t + 16 * i);
+    const uint32_t sp[4] = {__byte_perm(w.x, w.z, 0x5410), __byte_perm(w.x, w.z, 0x7632), __byte_perm(w.y, w.w, 0x5410),
+                            __byte_perm(w.y, w.w, 0x7632)};
+#pragma unroll
+    for (int k = 0; k < 4; ++k) {
+      qp[4 * i + k] = hmul2_u32(qh[4 * i + k], sp[k]);
+      ql[4 * i + k] = hfma2_neg_u32(qh[4 * i + k], sp[k], qp[4 * i + k]);
+    }
+  }
+  // zero-point term sum_c Q'[c] * zero[c], as one more MMA chain whose 16 rows are all the zero row
+  float zc[4] = {0.f, 0.f, 0.f, 0.f};
+  {
+    const uint4 za = *reinterpret_cast<const uint4*>(kz + 32 * t);
+    const uint4 zb = *reinterpret_cast<const uint4*>(kz + 32 * t + 16);
+    const uint32_t z[8] = {za.x, za.y, za.z, za.w, zb.x, zb.y, zb.z, zb.w};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t x = __byte_perm(z[2 * i], z[2 * i + 1], 0x5410);  // z0 z1 z4 z5
+      const uint32_t y = __byte_perm(z[2 * i], z[2 * i + 1], 0x7632);  // z2 z3 z6 z7
+      const uint32_t r0 = x & 0x00FF00FFu, r1 = __byte_perm(x, 0u, 0x4341);
+      const uint32_t r2 = y & 0x00FF00FFu, r3 = __byte_perm(y, 0u, 0x4341);
+      mma_f16(zc, r0, r0, r2, r2, qp[4 * i + 0], qp[4 * i + 2]);
+      mma_f16(zc, r1, r1, r3, r3, qp[4 * i + 1], qp[4 * i + 3]);
+      mma_f16(zc, r0, r0, r2, r2, ql[4 * i + 0], ql[4 * i + 2]);
+      mma_f16(zc, r1, r1, r3, r3, ql[4 * i + 1], ql[4 * i + 3]);
+    }
+  }
+  const float f24 = k2p24 * alpha, f20 = k2p20 * alpha;
+#pragma unroll
+  for (int j = 0; j < NT; ++j) {
+    const uint8_t* r = krows + (16 * j + pg) * 64 + 16 * t;
+    const uint4 ka = *reinterpret_cast<const uint4*>(r);
+    const uint4 kb = *reinterpret_cast<const uint4*>(r + 8 * 64);
+    const uint32_t wa[4] = {ka.x, ka.y, ka.z, ka.w}, wb[4] = {kb.x, kb.y, kb.z, kb.w};
+    float lo[4] = {-zc[0], -zc[1], -zc[2], -zc[3]}, hi[4] = {0.f, 0.f, 0.f, 0.f};
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      const uint32_t a8 = wa[i] >> 8, b8 = wb[i] >> 8;
+      const uint32_t l0 = wa[i] & kMaskLo, l1 = wb[i] & kMaskLo, l2 = a8 & kMaskLo, l3 = b8 & kMaskLo;
+      const uint32_t h0 = wa[i] & kMaskHi, h1 = wb[i] & kMaskHi, h2 = a8 & kMaskHi, h3 = b8 & kMaskHi;
+      mma_f16(lo, l0, l1, l2, l3, qp[4 * i + 0], qp[4 * i + 2]);
+      mma_f16(hi, h0, h1, h2, h3, qp[4 * i + 1], qp[4 * i + 3]);
+      mma_f16(lo, l0, l1, l2, l3, ql[4 * i + 0], ql[4 * i + 2]);
+      mma_f16(hi, h0, h1, h2, h3, ql[4 * i + 1], ql[4 * i + 3]);
+    }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) s[j][c] = fmaf(lo[c], f24, hi[c] * f20);
+  }
+}
+
+__device__ __forceinline__ void mask_scores(float (&s)[4], int row_a, int lo, int hi) {
+  if (row_a < lo || row_a >= hi) s[0] = s[1] = -INFINITY;
+  if (row_a + 8 < lo || row_a + 8 >= hi) s[2] = s[3] = -INFINITY;
+}
+
+// O^T += V^T P^T for one 16-token tile of INT4 values (codes as subnormals, scale folded into P).
+__device__ __forceinline__ void pv_int4(WarpState& st, const uint8_t* vrows, const float* vscale, float (&p)[4],
+                                        int g, int t, int pg, int row0, int lo, int hi, bool partial) {
+  float sa = vscale[pg], sb = vscale[pg + 8];
+  if (partial) {
+    if (row0 + pg < lo || row0 + pg >= hi) sa = 0.f;
+    if (row0 + pg + 8 < lo || row0 + pg + 8 >= hi) sb = 0.f;
+  }
+  const uint32_t ha = pack_f16x2(p[0] * sa, p[1] * sa), hb = pack_f16x2(p[2] * sb, p[3] * sb);
+  {
+    const float2 fa = __half22float2(*reinterpret_cast<const __half2*>(&ha));
+    const float2 fb = __half22float2(*reinterpret_cast<const __half2*>(&hb));
+    st.lp[0] += fa.x + fb.x;
+    st.lp[1] += fa.y + fb.y;
+  }
+  const uint32_t b0 = movmatrix_trans(ha), b1 = movmatrix_trans(hb);
+  const int t0 = 2 * t + (t & 1), t1 = 2 * t + 1 - (t & 1);
+  const uint8_t* base = vrows + 8 * g;
+  const uint2 w0 = *reinterpret_cast<const uint2*>(base + t0 * 64);
+  const uint2 w1 = *reinterpret_cast<const uint2*>(base + t1 * 64);
+  const uint2 w2 = *reinterpret_cast<const uint2*>(base + (t0 + 8) * 64);
+  const uint2 w3 = *reinterpret_cast<const uint2*>(base + (t1 + 8) * 64);
+#pragma unroll
+  for (int hf = 0; hf < 2; ++hf) {
+    const uint32_t c0 = (hf ? w0.y : w0.x) ^ 0x88888888u, c1 = (hf ? w1.y : w1.x) ^ 0x88888888u;
+    const uint32_t c2 = (hf ? w2.y : w2.x) ^ 0x88888888u, c3 = (hf ? w3.y : w3.x) ^ 0x88888888u;
+    const uint32_t xa = __byte_perm(c0, c1, 0x5410), ya = __byte_perm(c0, c1, 0x7632);
+    const uint32_t xb = __byte_perm(c2, c3, 0x5410), yb = __byte_perm(c2, c3, 0x7632);
+    mma_f16(st.o[4 * hf + 0], xa & kMaskLo, xa & kMaskHi, xb & kMaskLo, xb & kMaskHi, b0, b1);
+    mma_f16(st.o[4 * hf + 1], (xa >> 8) & kMaskLo, (xa >> 8) & kMaskHi, (xb >> 8) & kMaskLo, (xb >> 8) & kMaskHi, b0, b1);
+    mma_f16(st.o[4 * hf + 2], ya & kMaskLo, ya & kMaskHi, yb & kMaskLo, yb & kMaskHi, b0, b1);
+    mma_f16(st.o[4 * hf + 3], (ya >> 8) & kMaskLo, (ya >> 8) & kMaskHi, (yb >> 8) & kMaskLo, (yb >> 8) & kMaskHi, b0, b1);
+  }
+}
+
+// (code - zero) * scale for the eight 2-bit fields of each half-word of x -> eight half2.
+__device__ __forceinline__ void dequant_crumbs(uint32_t x, const uint32_t (&zm)[5], const uint32_t (&sk)[5],
+                                               uint32_t (&v)[8]) {
+#pragma unroll
+  for (int i = 0; i < 5; ++i)
+    v[i] = hmul2_u32(hsub2_u32((x & (0x00030003u << (2 * i))) | 0x64006400u, zm[i]), sk[i]);
+  const uint32_t y = x >> 10;
+#pragma unroll
+  for (int i = 0; i < 3; ++i)
+    v[5 + i] = hmul2_u32(hsub2_u32((y & (0x00030003u << (2 * i))) | 0x64006400u, zm[i]), sk[i]);
+}
+
+// O^T += V^T P^T for one 16-token tile of INT2 values, dequantised in registers.
+__device__ __forceinline__ void pv_int2(WarpState& st, const uint8_t* vrows, const uint8_t* vscale, const uint8_t* vzero,
+                                        const DecodeParams& p, float (&pr)[4], int g, int t, int row0, int lo, int hi,
+                                        bool partial) {
+  const uint32_t b0 = movmatrix_trans(pack_f16x2(pr[0], pr[1])), b1 = movmatrix_trans(pack_f16x2(pr[2], pr[3]));
+  const int t0 = 2 * t + (t & 1), t1 = 2 * t + 1 - (t & 1);
+  const int tok[4] = {t0, t1, t0 + 8, t1 + 8};
+  const int grp = (16 * g) >> p.group2_shift;
+  uint32_t w[4], sc[4], zp[4];
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    w[i] = *reinterpret_cast<const uint32_t*>(vrows + tok[i] * 32 + 4 * g);
+    sc[i] = *reinterpret_cast<const uint16_t*>(vscale + (tok[i] * p.groups2 + grp) * 2);
+    zp[i] = vzero[tok[i] * p.groups2 + grp];
+    if (partial && (row0 + tok[i] < lo || row0 + tok[i] >= hi)) { sc[i] = 0u; zp[i] = 0u; }
+  }
+  uint32_t va[16], vb[16];
+#pragma unroll
+  for (int pr2 = 0; pr2 < 2; ++pr2) {
+    const uint32_t s2 = sc[2 * pr2] | (sc[2 * pr2 + 1] << 16), z2 = zp[2 * pr2] | (zp[2 * pr2 + 1] << 16);
+    uint32_t zm[5], sk[5];
+    const uint32_t quarter[5] = {0x3C003C00u, 0x34003400u, 0x2C002C00u, 0x24002400u, 0x1C001C00u};  // 4^-i as half2
+#pragma unroll
+    for (int i = 0; i < 5; ++i) { zm[i] = 0x64006400u + (z2 << (2 * i)); sk[i] = i ? hmul2_u32(s2, quarter[i]) : s2; }
+    const uint32_t x = __byte_perm(w[2 * pr2], w[2 * pr2 + 1], 0x5410), y = __byte_perm(w[2 * pr2], w[2 * pr2 + 1], 0x7632);
+    uint32_t lo8[8], hi8[8];
+    dequant_crumbs(x, zm, sk, lo8);
+    dequant_crumbs(y, zm, sk, hi8);
+#pragma unroll
+    for (int i = 0; i < 8; ++i) {
+      if (pr2 == 0) { va[i] = lo8[i]; va[8 + i] = hi8[i]; } else { vb[i] = lo8[i]; vb[8 + i] = hi8[i]; }
+    }
+  }
+#pragma unroll
+  for (int j = 0; j < 8; ++j) mma_f16(st.o[j], va[2 * j], va[2 * j + 1], vb[2 * j], vb[2 * j + 1], b0, b1);
+}
+
+// O^T += V^T P^T for one 16-token tile of 16-bit values (rows of 256 bytes).
+template <bool BF16>
+__device__ __forceinline__ void pv_fp(WarpState& st, const uint8_t* vrows, float (&pr)[4], int g, int t) {
+  uint32_t bh0, bh1, bl0 = 0, bl1 = 0;
+  if (BF16) {  // P = P_hi + P_lo in bf16: two MMAs keep ~16 mantissa bits of P
+    const uint32_t ha = pack_bf16x2(pr[0], pr[1]), hb = pack_bf16x2(pr[2], pr[3]);
+    const uint32_t la = pack_bf16x2(pr[0] - __uint_as_float(ha << 16), pr[1] - __uint_as_float(ha & 0xffff0000u));
+    const uint32_t lb = pack_bf16x2(pr[2] - __uint_as_float(hb << 16), pr[3] - __uint_as_float(hb & 0xffff0000u));
+    bh0 = movmatrix_trans(ha); bh1 = movmatrix_trans(hb);
+    bl0 = movmatrix_trans(la); bl1 = movmatrix_trans(lb);
+  } else {
+    bh0 = movmatrix_trans(pack_f16x2(pr[0], pr[1])); bh1 = movmatrix_trans(pack_f16x2(pr[2], pr[3]));
+  }
+  const int t0 = 2 * t + (t & 1), t1 = 2 * t + 1 - (t & 1);
+  const uint8_t* base = vrows + 32 * g;
+#pragma unroll
+  for (int hf = 0; hf < 2; ++hf) {
+    const uint4 r0 = *reinterpret_cast<const uint4*>(base + t0 * 256 + 16 * hf);
+    const uint4 r1 = *reinterpret_cast<const uint4*>(base + t1 * 256 + 16 * hf);
+    const uint4 r2 = *reinterpret_cast<const uint4*>(base + (t0 + 8) * 256 + 16 * hf);
+    const uint4 r3 = *reinterpret_cast<const uint4*>(base + (t1 + 8) * 256 + 16 * hf);
+    const uint32_t a[4] = {r0.x, r0.y, r0.z, r0.w}, b[4] = {r1.x, r1.y, r1.z, r1.w};
+    const uint32_t c[4] = {r2.x, r2.y, r2.z, r2.w}, d[4] = {r3.x, r3.y, r3.z, r3.w};
+#pragma unroll
+    for (int q = 0; q < 4; ++q) {
+      const uint32_t a0 = __byte_perm(a[q], b[q], 0x5410), a1 = __byte_perm(a[q], b[q], 0x7632);
+      const uint32_t a2 = __byte_perm(c[q], d[q], 0x5410), a3 = __byte_perm(c[q], d[q], 0x7632);
+      if (BF16) {
+        mma_bf16(st.o[4 * hf + q], a0, a1, a2, a3, bh0, bh1);
+        mma_bf16(st.o[4 * hf + q], a0, a1, a2, a3, bl0, bl1);
+      } else {
+        mma_f16(st.o[4 * hf + q], a0, a1, a2, a3, bh0, bh1);
+      }
+    }
+  }
+}
+
+// Scores of one 16-token tile of 16-bit keys (residual window): exact products, fp32 accumulation.
+template <bool BF16>
+__device__ __forceinline__ void qk_fp(const uint8_t* krows, const uint16_t* qrow, int t, int pg, float scale,
+                                      float (&s)[4]) {
+  float acc[4] = {0.f, 0.f, 0.f, 0.f};
+  const uint8_t* ra = krows + pg * 256 + 64 * t;
+  const uint8_t* rb = ra + 8 * 256;
+#pragma unroll
+  for (int i = 0; i < 4; ++i) {
+    const uint4 ka = *reinterpret_cast<const uint4*>(ra + 16 * i);
+    const uint4 kb = *reinterpret_cast<const uint4*>(rb + 16 * i);
+    uint4 qq = make_uint4(0u, 0u, 0u, 0u);
+    if (qrow != nullptr) qq = __ldg(reinterpret_cast<const uint4*>(qrow + 32 * t + 8 * i));
+    if (BF16) {
+      mma_bf16(acc, ka.x, kb.x, ka.y, kb.y, qq.x, qq.y);
+      mma_bf16(acc, ka.z, kb.z, ka.w, kb.w, qq.z, qq.w);
+    } else {
+      mma_f16(acc, ka.x, kb.x, ka.y, kb.y, qq.x, qq.y);
+      mma_f16(acc, ka.z, kb.z, ka.w, kb.w, qq.z, qq.w);
+    }
+  }
+#pragma unroll
+  for (int c = 0; c < 4; ++c) s[c] = acc[c] * scale;
+}
+
+// ---------------------------------------------------------------------------
+// producer
+// ---------------------------------------------------------------------------
+__device__ __forceinline__ void copy_piece(uint8_t* dst, const uint8_t* src, int bytes, uint64_t* bar, int lane,
+                                           uint32_t& tx) {
+  if (bytes <= 0) return;
+  if ((((uintptr_t)src | (uintptr_t)smem_u32(dst) | (uint32_t)bytes) & 15u) == 0) {
+    if (lane == 0) { bulk_g2s(dst, src, (uint32_t)bytes, bar); tx += (uint32_t)bytes; }
+  } else {  // ragged edge: plain loads
+    for (int i = lane; i < bytes; i += 32) dst[i] = src[i];
+  }
+}
+__device__ __forceinline__ void zero_piece(uint8_t* dst, int bytes, int lane) {
+  for (int i = lane; i < bytes; i += 32) dst[i] = 0;
+}
+
+__device__ __forceinline__ void produce_tile(const DecodeParams& p, const Tile& tl, int b, int h, uint8_t* stage,
+                                             uint64_t* bar, int lane) {
+  uint32_t tx = 0;
+  const R2KCacheView& v = p.v;
+  const int nvalid = tl.hi - tl.lo;
+  if (tl.pool == 3) {
+    const size_t row = ((size_t)h * p.g.recent_capacity + tl.win) * 256;
+    copy_piece(stage + kOffV, (const uint8_t*)v.recent_k + (size_t)b * v.recent_k_bstride + row, nvalid * 256, bar, lane, tx);
+    copy_piece(stage + kOffV + kOffRecentV, (const uint8_t*)v.recent_v + (size_t)b * v.recent_v_bstride + row, nvalid * 256,
+               bar, lane, tx);
+    if (nvalid < kTR) {
+      zero_piece(stage + kOffV + nvalid * 256, (kTR - nvalid) * 256, lane);
+      zero_piece(stage + kOffV + kOffRecentV + nvalid * 256, (kTR - nvalid) * 256, lane);
+    }
+  } else {
+    const int len = tl.pool == 0 ? kTF : kTQ;
+    // keys: the whole window (always inside the arena: windows and capacity are multiples of the tile)
+    copy_piece(stage + kOffK, v.k_packed + (size_t)b * v.k_packed_bstride + ((size_t)h * p.g.k_capacity + tl.win) * 64,
+               len * 64, bar, lane, tx);
+    const int blk0 = tl.win >> p.kblock_shift;
+    const int nblk = max(1, len >> p.kblock_shift);
+    const size_t meta = (size_t)h * (p.g.k_capacity >> p.kblock_shift) + blk0;
+    copy_piece(stage + kOffKS, (const uint8_t*)v.k_scale + (size_t)b * v.k_scale_bstride + meta * 256, nblk * 256, bar, lane, tx);
+    copy_piece(stage + kOffKZ, v.k_zero + (size_t)b * v.k_zero_bstride + meta * 128, nblk * 128, bar, lane, tx);
+    // values: only rows of this pool; rows of the window outside it are cleared
+    uint8_t* vreg = stage + kOffV;
+    if (tl.pool == 0) {
+      const size_t row = (size_t)h * p.g.fp_capacity + (tl.win + tl.lo - p.g.k_off_fp);
+      copy_piece(vreg + tl.lo * 256, (const uint8_t*)v.fp_v + (size_t)b * v.fp_v_bstride + row * 256, nvalid * 256, bar, lane, tx);
+      if (nvalid < len) { zero_piece(vreg, tl.lo * 256, lane); zero_piece(vreg + tl.hi * 256, (len - tl.hi) * 256, lane); }
+    } else if (tl.pool == 1) {
+      const size_t row = (size_t)h * p.g.i4_capacity + (tl.win + tl.lo - p.g.k_off_i4);
+      copy_piece(vreg + tl.lo * 64, v.i4_packed + (size_t)b * v.i4_packed_bstride + row * 64, nvalid * 64, bar, lane, tx);
+      copy_piece(vreg + kOffI4Scale + tl.lo * 4, (const uint8_t*)v.i4_scale + (size_t)b * v.i4_scale_bstride + row * 4,
+                 nvalid * 4, bar, lane, tx);
+      if (nvalid < len) {
+        zero_piece(vreg + kOffI4Scale, tl.lo * 4, lane);
+        zero_piece(vreg + kOffI4Scale + tl.hi * 4, (len - tl.hi) * 4, lane);
+      }
+    } else {
+      const size_t row = (size_t)h * p.g.i2_capacity + (tl.win + tl.lo - p.g.k_off_i2);
+      const int g2 = p.groups2;
+      copy_piece(vreg + tl.lo * 32, v.i2_packed + (size_t)b * v.i2_packed_bstride + row * 32, nvalid * 32, bar, lane, tx);
+      copy_piece(vreg + kOffI2Scale + tl.lo * g2 * 2, (const uint8_t*)v.i2_scale + (size_t)b * v.i2_scale_bstride + row * g2 * 2,
+                 nvalid * g2 * 2, bar, lane, tx);
+      copy_piece(vreg + kOffI2Zero + tl.lo * g2, v.i2_zero + (size_t)b * v.i2_zero_bstride + row * g2, nvalid * g2, bar, lane, tx);
+      if (nvalid < len) {
+        zero_piece(vreg + kOffI2Scale, tl.lo * g2 * 2, lane);
+        zero_piece(vreg + kOffI2Scale + tl.hi * g2 * 2, (len - tl.hi) * g2 * 2, lane);
+      }
+    }
+  }
+  __syncwarp();
+  if (lane == 0) mbar_arrive_expect_tx(bar, tx);
+}
+
+}  // namespace
+
+// ---------------------------------------------------------------------------
+// kernel
+// ---------------------------------------------------------------------------
+template <bool BF16>
+__global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const __grid_constant__ DecodeParams p) {
+  extern __shared__ __align__(1024) uint8_t smem[];
+  uint8_t* stages = smem;
+  float* scratch = reinterpret_cast<float*>(smem + kStages * kStageBytes);
+  uint64_t* full_bar = reinterpret_cast<uint64_t*>(smem + kStages * kStageBytes + kScratchBytes);
+  uint64_t* empty_bar = full_bar + kStages;
+  int* flags = reinterpret_cast<int*>(empty_bar + kStages);  // [0] last-arriver flag
+
+  const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
+  const int cta = blockIdx.x;
+  if (threadIdx.x == 0) {
+    for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], kNW); }
+    mbar_fence_init();
+  }
+  __syncthreads();
+
+  const int64_t x0 = cta_cost_begin(p, cta), x1 = cta_cost_begin(p, cta + 1);
+  int bh_lo = (int)(x0 / p.c_bh), bh_hi = (int)((x1 - 1) / p.c_bh);
+  if (bh_hi > p.bh_total - 1) bh_hi = p.bh_total - 1;
+  const bool has_append = p.app_k != nullptr;
+
+  int stage = 0;
+  uint32_t phase = 0;
+
+  if (warp == kNW) {
+    // ------------------------------ producer ------------------------------
+    bool alive = true;
+    for (int bh = bh_lo; bh <= bh_hi && alive; ++bh) {
+      const int b = bh / p.g.num_kv_heads, h = bh - b * p.g.num_kv_heads;
+      int u0, u1;
+      unit_range(p, cta, bh, u0, u1);
+      const int rlen = *reinterpret_cast<const int*>((const uint8_t*)p.v.recent_len + (size_t)b * p.v.recent_len_bstride) +
+                       (has_append ? 1 : 0);
+      for (int u = u0; u < u1; ++u) {
+        const Tile tl = tile_of(p, u);
+        if (tl.pool == 3 && tl.win >= rlen) continue;
+        if (!mbar_wait(&empty_bar[stage], phase ^ 1u)) {
+          if (lane == 0) atomicExch(p.err, R2K_ERR_DEVICE_TIMEOUT);
+          alive = false;
+          break;
+        }
+        produce_tile(p, tl, b, h, stages + stage * kStageBytes, &full_bar[stage], lane);
+        if (++stage == kStages) { stage = 0; phase ^= 1u; }
+      }
+    }
+    return;
+  }
+
+  // -------------------------------- consumers --------------------------------
+  const int g = lane >> 2, t = lane & 3, pg = pi_row(g);
+  bool alive = true;
+  WarpState st;
+
+  for (int bh = bh_lo; bh <= bh_hi; ++bh) {
+    const int b = bh / p.g.num_kv_heads, h = bh - b * p.g.num_kv_heads;
+    int u0, u1;
+    unit_range(p, cta, bh, u0, u1);
+    const int rlen0 = *reinterpret_cast<const int*>((const uint8_t*)p.v.recent_len + (size_t)b * p.v.recent_len_bstride);
+    const int rlen = rlen0 + (has_append ? 1 : 0);
+    state_reset(st);
+
+    // query fragments of head g of this KV group, channels 32t..32t+31
+    const uint16_t* qrow = nullptr;
+    uint32_t qh[16];
+    if (g < p.gqa) qrow = reinterpret_cast<const uint16_t*>(p.q) + ((size_t)b * p.g.num_q_heads + h * p.gqa + g) * kD;
+#pragma unroll
+    for (int i = 0; i < 4; ++i) {
+      uint4 raw = make_uint4(0u, 0u, 0u, 0u);
+      if (qrow != nullptr) raw = __ldg(reinterpret_cast<const uint4*>(qrow + 32 * t + 8 * i));
+      const uint32_t wv[4] = {raw.x, raw.y, raw.z, raw.w};
+      float f[8];
+#pragma unroll
+      for (int e = 0; e < 8; ++e) f[e] = elem_to_float<BF16>((uint16_t)(wv[e >> 1] >> (16 * (e & 1))));
+#pragma unroll
+      for (int k = 0; k < 4; ++k) qh[4 * i + k] = pack_f16x2(f[k], f[k + 4]);
+    }
+
+    for (int u = u0; u < u1; ++u) {
+      const Tile tl = tile_of(p, u);
+      if (tl.pool == 3 && tl.win >= rlen) continue;
+      if (alive && !mbar_wait(&full_bar[stage], phase)) {
+        if (lane == 0) atomicExch(p.err, R2K_ERR_DEVICE_TIMEOUT);
+        alive = false;
+      }
+      if (alive) {
+        uint8_t* sb = stages + stage * kStageBytes;
+        if (tl.pool == 1 || tl.pool == 2) {
+          const int r0 = 32 * warp;  // this warp's key block inside the window
+          const int lo = max(tl.lo - r0, 0), hi = min(tl.hi - r0, 32);
+          if (hi > lo) {
+            const bool partial = (lo > 0) | (hi < 32);
+            const int blk = ((tl.win + r0) >> p.kblock_shift) - (tl.win >> p.kblock_shift);
+            float s[2][4];
+            qk_int4<2>(sb + kOffK + r0 * 64, sb + kOffKS + blk * 256, sb + kOffKZ + blk * 128, qh, t, pg, p.qscale, s);
+            if (partial) { mask_scores(s[0], pg, lo, hi); mask_scores(s[1], 16 + pg, lo, hi); }
+            softmax_update<2>(st, s);
+            if (tl.pool == 1) {
+              set_units(st, 1);
+#pragma unroll
+              for (int j = 0; j < 2; ++j)
+                pv_int4(st, sb + kOffV + (r0 + 16 * j) * 64, reinterpret_cast<const float*>(sb + kOffV + kOffI4Scale) + r0 + 16 * j,
+                        s[j], g, t, pg, 16 * j, lo, hi, partial);
+            } else {
+              set_units(st, 0);
+#pragma unroll
+              for (int j = 0; j < 2; ++j)
+                pv_int2(st, sb + kOffV + (r0 + 16 * j) * 32, sb + kOffV + kOffI2Scale + (r0 + 16 * j) * p.groups2 * 2,
+                        sb + kOffV + kOffI2Zero + (r0 + 16 * j) * p.groups2, p, s[j], g, t, 16 * j, lo, hi, partial);
+            }
+          }
+        } else if (tl.pool == 0) {
+          const int r0 = 16 * warp;
+          const int lo = max(tl.lo - r0, 0), hi = min(tl.hi - r0, 16);
+          if (hi > lo) {
+            const int blk = ((tl.win + r0) >> p.kblock_shift) - (tl.win >> p.kblock_shift);
+            float s[1][4];
+            qk_int4<1>(sb + kOffK + r0 * 64, sb + kOffKS + blk * 256, sb + kOffKZ + blk * 128, qh, t, pg, p.qscale, s);
+            if ((lo > 0) | (hi < 16)) mask_scores(s[0], pg, lo, hi);
+            softmax_update<1>(st, s);
+            set_units(st, 0);
+            pv_fp<BF16>(st, sb + kOffV + r0 * 256, s[0], g, t);
+          }
+        } else if (warp < 2) {
+          const int r0 = 16 * warp;
+          const int hi = min(rlen - tl.win - r0, 16);
+          if (hi > 0) {
+            const int app_row = rlen0 - tl.win - r0;  // ring row that receives the appended token, relative to this slice
+            if (has_append && app_row >= 0 && app_row < 16) {
+              const size_t off = ((size_t)b * p.g.num_kv_heads + h) * 256 + 8 * lane;
+              *reinterpret_cast<uint2*>(sb + kOffV + (r0 + app_row) * 256 + 8 * lane) =
+                  __ldg(reinterpret_cast<const uint2*>((const uint8_t*)p.app_k + off));
+              *reinterpret_cast<uint2*>(sb + kOffV + kOffRecentV + (r0 + app_row) * 256 + 8 * lane) =
+                  __ldg(reinterpret_cast<const uint2*>((const uint8_t*)p.app_v + off));
+              __syncwarp();
+            }
+            float s[1][4];
+            qk_fp<BF16>(sb + kOffV + r0 * 256, qrow, t, pg, p.qscale, s[0]);
+            if (hi < 16) mask_scores(s[0], pg, 0, hi);
+            softmax_update<1>(st, s);
+            set_units(st, 0);
+            pv_fp<BF16>(st, sb + kOffV + kOffRecentV + r0 * 256, s[0], g, t);
+          }
+        }
+        __syncwarp();
+        if (lane == 0) mbar_arrive(&empty_bar[stage]);
+      }
+      if (++stage == kStages) { stage = 0; phase ^= 1u; }
+    }
+
+    // ---- this CTA's partial for (b, h): merge the four warps through shared memory ----
+    set_units(st, 0);
+#pragma unroll
+    for (int d = 4; d < 32; d <<= 1) {
+      st.l[0] += __shfl_xor_sync(0xffffffffu, st.l[0], d);
+      st.l[1] += __shfl_xor_sync(0xffffffffu, st.l[1], d);
+      st.lp[0] += __shfl_xor_sync(0xffffffffu, st.lp[0], d);
+      st.lp[1] += __shfl_xor_sync(0xffffffffu, st.lp[1], d);
+    }
+    {
+      float* mine = scratch + warp * kSlotFloats;
+      float* r0 = mine + (2 * t) * kRowFloats;
+      float* r1 = r0 + kRowFloats;
+      const float c0 = 8.f * st.lp[0], c1 = 8.f * st.lp[1];  // INT4 value codes were fed as code+8
+#pragma unroll
+      for (int j = 0; j < 8; ++j) {
+        *reinterpret_cast<float2*>(r0 + 4 + 16 * g + 2 * j) = make_float2(st.o[j][0] - c0, st.o[j][2] - c0);
+        *reinterpret_cast<float2*>(r1 + 4 + 16 * g + 2 * j) = make_float2(st.o[j][1] - c1, st.o[j][3] - c1);
+      }
+      if (g == 0) { r0[0] = st.m[0]; r0[1] = st.l[0]; r1[0] = st.m[1]; r1[1] = st.l[1]; }
+    }
+    named_bar_sync(1, kConsumers);
+    const int part0 = first_cta_of(p, bh);
+    const int nparts = last_cta_of(p, bh) - part0 + 1;
+    float* slot = p.partials + ((size_t)bh * p.parts_cap + (cta - part0)) * kSlotFloats;
+    {
+      const int hh = threadIdx.x >> 4, sub = threadIdx.x & 15;  // 16 threads per head, 8 dims each
+      float mw[kNW], mx = -INFINITY;
+#pragma unroll
+      for (int w = 0; w < kNW; ++w) { mw[w] = scratch[w * kSlotFloats + hh * kRowFloats]; mx = fmaxf(mx, mw[w]); }
+      float4 a0 = make_float4(0.f, 0.f, 0.f, 0.f), a1 = a0;
+      float lsum = 0.f;
+#pragma unroll
+      for (int w = 0; w < kNW; ++w) {
+        const float wgt = (mw[w] == -INFINITY) ? 0.f : ex2_approx(mw[w] - mx);
+        const float* row = scratch + w * kSlotFloats + hh * kRowFloats;
+        const float4 v0 = *reinterpret_cast<const float4*>(row + 4 + 8 * sub);
+        const float4 v1 = *reinterpret_cast<const float4*>(row + 8 + 8 * sub);
+        a0.x += wgt * v0.x; a0.y += wgt * v0.y; a0.z += wgt * v0.z; a0.w += wgt * v0.w;
+        a1.x += wgt * v1.x; a1.y += wgt * v1.y; a1.z += wgt * v1.z; a1.w += wgt * v1.w;
+        lsum += wgt * row[1];
+      }
+      float* orow = slot + hh * kRowFloats;
+      __stcg(reinterpret_cast<float4*>(orow + 4 + 8 * sub), a0);
+      __stcg(reinterpret_cast<float4*>(orow + 8 + 8 * sub), a1);
+      if (sub == 0) __stcg(reinterpret_cast<float2*>(orow), make_float2(mx, lsum));
+    }
+    __threadfence();
+    named_bar_sync(1, kConsumers);
+    if (threadIdx.x == 0) {
+      const int ticket = atomicAdd(&p.bh_counter[bh], 1);
+      flags[0] = (ticket == nparts - 1);
+      __threadfence();
+    }
+    named_bar_sync(1, kConsumers);
+    if (flags[0]) {
+      // ---- last arriver: exact merge of all partials of (b, h), epilogue, fused append ----
+      const float* base = p.partials + (size_t)bh * p.parts_cap * kSlotFloats;
+      for (int hh = warp; hh < p.gqa; hh += kNW) {
+        float mx = -INFINITY;
+        for (int q = lane; q < nparts; q += 32) mx = fmaxf(mx, __ldcg(base + (size_t)q * kSlotFloats + hh * kRowFloats));
+#pragma unroll
+        for (int d = 1; d < 32; d <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
+        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+        float lsum = 0.f;
+        for (int q = 0; q < nparts; ++q) {
+          const float* row = base + (size_t)q * kSlotFloats + hh * kRowFloats;
+          const float2 ml = __ldcg(reinterpret_cast<const float2*>(row));
+          const float wgt = (ml.x == -INFINITY) ? 0.f : ex2_approx(ml.x - mx);
+          const float4 v = __ldcg(reinterpret_cast<const float4*>(row + 4 + 4 * lane));
+          acc.x += wgt * v.x; acc.y += wgt * v.y; acc.z += wgt * v.z; acc.w += wgt * v.w;
+          lsum += wgt * ml.y;
+        }
+        const size_t orow = (size_t)b * p.g.num_q_heads + h * p.gqa + hh;
+        if (p.flags & R2K_FLAG_OUT_STATE) {
+          float* o = reinterpret_cast<float*>(p.out) + orow * 130;
+          if (lane == 0) { o[0] = mx * kLn2; o[1] = lsum; }
+          o[2 + 4 * lane + 0] = acc.x; o[2 + 4 * lane + 1] = acc.y; o[2 + 4 * lane + 2] = acc.z; o[2 + 4 * lane + 3] = acc.w;
+        } else {
+          const float inv = 1.f / lsum;
+          float r[4] = {acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv};
+          if (p.flags & R2K_FLAG_OUTPUT_HADAMARD) {
+#pragma unroll
+            for (int e = 0; e < 4; ++e)  // round through the element type first, as the reference does
+              r[e] = BF16 ? __bfloat162float(__float2bfloat16_rn(r[e])) : __half2float(__float2half_rn(r[e]));
+            float a = r[0] + r[1], bq = r[0] - r[1], c = r[2] + r[3], d = r[2] - r[3];
+            r[0] = a + c; r[1] = bq + d; r[2] = a - c; r[3] = bq - d;
+#pragma unroll
+            for (int sft = 1; sft < 32; sft <<= 1) {
+#pragma unroll
+              for (int e = 0; e < 4; ++e) {
+                const float o2 = __shfl_xor_sync(0xffffffffu, r[e], sft);
+                r[e] = (lane & sft) ? (o2 - r[e]) : (r[e] + o2);
+              }
+            }
+#pragma unroll
+            for (int e = 0; e < 4; ++e) r[e] *= 0.08838834764831845f;
+          }
+          if (p.flags & R2K_FLAG_OUT_F32) {
+            *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + orow * kD + 4 * lane) = make_float4(r[0], r[1], r[2], r[3]);
+          } else {
+            uint2 pk;
+            if (BF16) { pk.x = pack_bf16x2(r[0], r[1]); pk.y = pack_bf16x2(r[2], r[3]); }
+            else { pk.x = pack_f16x2(r[0], r[1]); pk.y = pack_f16x2(r[2], r[3]); }
+            *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(p.out) + orow * kD + 4 * lane) = pk;
+          }
+        }
+      }
+      if (has_append && warp == 0) {  // ring row rlen0 of head h
+        const size_t src = ((size_t)b * p.g.num_kv_heads + h) * 256 + 8 * lane;
+        const size_t dst = ((size_t)h * p.g.recent_capacity + rlen0) * 256 + 8 * lane;
+        *reinterpret_cast<uint2*>((uint8_t*)p.v.recent_k + (size_t)b * p.v.recent_k_bstride + dst) =
+            __ldg(reinterpret_cast<const uint2*>((const uint8_t*)p.app_k + src));
+        *reinterpret_cast<uint2*>((uint8_t*)p.v.recent_v + (size_t)b * p.v.recent_v_bstride + dst) =
+            __ldg(reinterpret_cast<const uint2*>((const uint8_t*)p.app_v + src));
+      }
+      named_bar_sync(1, kConsumers);
+      if (threadIdx.x == 0) {
+        p.bh_counter[bh] = 0;
+        __threadfence();
+        const int done = atomicAdd(&p.req_counter[b], 1);
+        if (done == p.g.num_kv_heads - 1) {  // every head of request b is merged: nobody reads recent_len[b] any more
+          p.req_counter[b] = 0;
+          if (has_append) {
+            const int64_t gi = p.app_idx ? p.app_idx[2 * b] : p.app_global;
+            const int64_t lp = p.app_idx ? p.app_idx[2 * b + 1] : p.app_logical;
+            *reinterpret_cast<int64_t*>((uint8_t*)p.v.recent_global + (size_t)b * p.v.recent_global_bstride + 8 * (size_t)rlen0) = gi;
+            *reinterpret_cast<int64_t*>((uint8_t*)p.v.recent_logical + (size_t)b * p.v.recent_logical_bstride + 8 * (size_t)rlen0) = lp;
+            *reinterpret_cast<int*>((uint8_t*)p.v.recent_len + (size_t)b * p.v.recent_len_bstride) = rlen0 + 1;
+            *reinterpret_cast<int64_t*>((uint8_t*)p.v.recent_page_lengths + (size_t)b * p.v.recent_page_lengths_bstride +
+                                        8 * (size_t)(rlen0 / p.g.page_size)) = rlen0 % p.g.page_size + 1;
+          }
+        }
+      }
+    }
+    named_bar_sync(1, kConsumers);  // scratch and flags are reused by the next (request, kv head)
+  }
+}
+
+// ---------------------------------------------------------------------------
+// cross-shard merge of un-normalised states
+// ---------------------------------------------------------------------------
+__global__ void merge_states_kernel(const float* __restrict__ states, int num_states, int64_t state_stride, int rows,
+                                    int dtype, void* out, uint32_t flags) {
+  const int row = blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  float mx = -INFINITY;
+  for (int s = 0; s < num_states; ++s) mx = fmaxf(mx, states[s * state_stride + (int64_t)row * 130]);
+  float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
+  float lsum = 0.f;
+  for (int s = 0; s < num_states; ++s) {
+    const float* st = states + s * state_stride + (int64_t)row * 130;
+    const float wgt = (st[0] == -INFINITY) ? 0.f : __expf(st[0] - mx);
+    const float2 v0 = *reinterpret_cast<const float2*>(st + 2 + 4 * lane);
+    const float2 v1 = *reinterpret_cast<const float2*>(st + 4 + 4 * lane);
+    acc.x += wgt * v0.x; acc.y += wgt * v0.y; acc.z += wgt * v1.x; acc.w += wgt * v1.y;
+    lsum += wgt * st[1];
+  }
+  const float inv = 1.f / lsum;
+  float r[4] = {acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv};
+  const bool bf16 = dtype == R2K_DTYPE_BF16;
+  if (flags & R2K_FLAG_OUTPUT_HADAMARD) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) r[e] = bf16 ? __bfloat162float(__float2bfloat16_rn(r[e])) : __half2float(__float2half_rn(r[e]));
+    float a = r[0] + r[1], bq = r[0] - r[1], c = r[2] + r[3], d = r[2] - r[3];
+    r[0] = a + c; r[1] = bq + d; r[2] = a - c; r[3] = bq - d;
+#pragma unroll
+    for (int sft = 1; sft < 32; sft <<= 1) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float o2 = __shfl_xor_sync(0xffffffffu, r[e], sft);
+        r[e] = (lane & sft) ? (o2 - r[e]) : (r[e] + o2);
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) r[e] *= 0.08838834764831845f;
+  }
+  if (flags & R2K_FLAG_OUT_F32) {
+    *reinterpret_cast<float4*>(reinterpret_cast<float*>(out) + (int64_t)row * kD + 4 * lane) = make_float4(r[0], r[1], r[2], r[3]);
+  } else {
+    uint2 pk;
+    if (bf16) { pk.x = pack_bf16x2(r[0], r[1]); pk.y = pack_bf16x2(r[2], r[3]); }
+    else { pk.x = pack_f16x2(r[0], r[1]); pk.y = pack_f16x2(r[2], r[3]); }
+    *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(out) + (int64_t)row * kD + 4 * lane) = pk;
+  }
+}
+
+}  // namespace r2k

@@ -1,0 +1,394 @@
+// extern "C" surface of libr2k_b200.so: validation, launch geometry, launches.
+// No torch types, no allocation, no synchronisation (except r2k_decode_device_status).
+#include <atomic>
+#include <cstring>
+
+#include "decode_kernel.cuh"
+#include "pack_kernels.cuh"
+#include "r2k_b200.h"
+
+namespace r2k {
+namespace {
+
+std::atomic<uint64_t> g_launches{0};
+
+struct DeviceInfo {
+  int sms = 0;
+  bool attr_set = false;
+};
+DeviceInfo g_dev[64];
+
+int device_info(DeviceInfo** out) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return R2K_ERR_CUDA;
+  DeviceInfo& d = g_dev[dev];
+  if (d.sms == 0) {
+    int sms = 0;
+    if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) return R2K_ERR_CUDA;
+    d.sms = sms;
+  }
+  *out = &d;
+  return R2K_OK;
+}
+
+inline bool pow2_in(int v, int a, int b, int c) { return v == a || v == b || v == c; }
+inline int ilog2(int v) { int s = 0; while ((1 << s) < v) ++s; return s; }
+inline bool aligned16(const void* p) { return (reinterpret_cast<uintptr_t>(p) & 15u) == 0; }
+
+int check_geom(const R2KGeom* g) {
+  if (g == nullptr) return R2K_ERR_NULL;
+  if (g->head_dim != kD || g->batch < 1 || g->num_kv_heads < 1 || g->num_q_heads < 1) return R2K_ERR_GEOMETRY;
+  if (g->num_q_heads % g->num_kv_heads || g->num_q_heads / g->num_kv_heads > 8) return R2K_ERR_GEOMETRY;
+  if (g->dtype != R2K_DTYPE_BF16 && g->dtype != R2K_DTYPE_FP16) return R2K_ERR_GEOMETRY;
+  if (!pow2_in(g->k_block, 32, 64, 128) || !pow2_in(g->v2_group, 32, 64, 128) || !pow2_in(g->page_size, 16, 32, 64))
+    return R2K_ERR_GEOMETRY;
+  if (g->n_fp < 0 || g->n_i4 < 0 || g->n_i2 < 0 || g->recent_capacity < 0) return R2K_ERR_GEOMETRY;
+  if (g->k_capacity < 0 || g->k_capacity % 128) return R2K_ERR_GEOMETRY;
+  if (g->k_off_fp < 0 || g->k_off_i4 < g->k_off_fp + g->n_fp || g->k_off_i2 < g->k_off_i4 + g->n_i4 ||
+      g->k_off_i2 + g->n_i2 > g->k_capacity)
+    return R2K_ERR_GEOMETRY;
+  if (g->n_fp > g->fp_capacity || g->n_i4 > g->i4_capacity || g->n_i2 > g->i2_capacity) return R2K_ERR_CAPACITY;
+  if (g->recent_capacity % g->page_size) return R2K_ERR_GEOMETRY;
+  return R2K_OK;
+}
+
+int windows(int a0, int n, int tile, int* first) {
+  *first = a0 / tile * tile;
+  if (n <= 0) return 0;
+  return (a0 + n + tile - 1) / tile - a0 / tile;
+}
+
+// Everything the kernel derives from the geometry; shared by workspace sizing and the launch.
+int derive(const R2KGeom* g, DecodeParams* p) {
+  DeviceInfo* dev;
+  int rc = device_info(&dev);
+  if (rc) return rc;
+  std::memset(p, 0, sizeof(*p));
+  p->g = *g;
+  p->gqa = g->num_q_heads / g->num_kv_heads;
+  p->bh_total = g->batch * g->num_kv_heads;
+  p->nF = windows(g->k_off_fp, g->n_fp, kTF, &p->wF0);
+  p->n4 = windows(g->k_off_i4, g->n_i4, kTQ, &p->w40);
+  p->n2 = windows(g->k_off_i2, g->n_i2, kTQ, &p->w20);
+  p->nR = (g->recent_capacity + kTR - 1) / kTR;
+  p->units = p->nF + p->n4 + p->n2 + p->nR;
+  if (p->units == 0) return R2K_ERR_EMPTY;
+  const int g2 = kD / g->v2_group;
+  p->cF = (int64_t)kTF * (64 + 256 + 384 / g->k_block);
+  p->c4 = (int64_t)kTQ * (64 + 68 + 384 / g->k_block);
+  p->c2 = (int64_t)kTQ * (64 + 32 + 3 * g2 + 384 / g->k_block);
+  p->cR = (int64_t)kTR * 512;
+  p->c_bh = p->nF * p->cF + p->n4 * p->c4 + p->n2 * p->c2 + p->nR * p->cR;
+  p->c_total = p->c_bh * p->bh_total;
+  const int64_t total_units = (int64_t)p->units * p->bh_total;
+  const int64_t cap = (int64_t)dev->sms * kCtasPerSm;
+  p->grid = (int)(total_units < cap ? total_units : cap);
+  p->parts_cap = (p->grid + p->bh_total - 1) / p->bh_total + 1;
+  p->groups2 = g2;
+  p->group2_shift = ilog2(g->v2_group);
+  p->kblock_shift = ilog2(g->k_block);
+  const float sm = g->sm_scale > 0.f ? g->sm_scale : 0.08838834764831845f;
+  p->qscale = sm * 1.4426950408889634f;
+  return R2K_OK;
+}
+
+size_t counters_bytes(const DecodeParams& p) {
+  const size_t n = (size_t)(p.bh_total + p.g.batch) * sizeof(int);
+  return (n + 255) / 256 * 256;
+}
+
+template <bool BF16>
+int launch_pack_k(const PackArgs& a, int batch, uint8_t* packed, void* scale, uint8_t* zero, int64_t pb, int64_t sb, int64_t zb,
+                  int k_block, cudaStream_t st) {
+  const int64_t first = a.dst_start / k_block, last = (a.dst_start + a.count - 1) / k_block;
+  dim3 grid((unsigned)(last - first + 1), (unsigned)a.num_heads, (unsigned)batch);
+  pack_k_int4_kernel<BF16><<<grid, 64, 0, st>>>(a, packed, reinterpret_cast<__half*>(scale), zero, pb, sb, zb, k_block, first);
+  ++g_launches;
+  return cudaGetLastError() == cudaSuccess ? R2K_OK : R2K_ERR_CUDA;
+}
+template <bool BF16>
+int launch_pack_v2(const PackArgs& a, int batch, uint8_t* packed, void* scale, uint8_t* zero, int64_t pb, int64_t sb, int64_t zb,
+                   int group, cudaStream_t st) {
+  dim3 grid((unsigned)((a.count + 3) / 4), (unsigned)a.num_heads, (unsigned)batch);
+  pack_v_int2_kernel<BF16><<<grid, 128, 0, st>>>(a, packed, reinterpret_cast<__half*>(scale), zero, pb, sb, zb, group);
+  ++g_launches;
+  return cudaGetLastError() == cudaSuccess ? R2K_OK : R2K_ERR_CUDA;
+}
+
+RingArgs ring_args(const R2KGeom* g, const R2KCacheView* v) {
+  RingArgs r;
+  r.recent_k = reinterpret_cast<uint8_t*>(v->recent_k);
+  r.recent_v = reinterpret_cast<uint8_t*>(v->recent_v);
+  r.recent_len = v->recent_len;
+  r.recent_global = v->recent_global;
+  r.recent_logical = v->recent_logical;
+  r.recent_page_lengths = v->recent_page_lengths;
+  r.k_bstride = v->recent_k_bstride; r.v_bstride = v->recent_v_bstride; r.len_bstride = v->recent_len_bstride;
+  r.global_bstride = v->recent_global_bstride; r.logical_bstride = v->recent_logical_bstride;
+  r.page_bstride = v->recent_page_lengths_bstride;
+  r.num_heads = g->num_kv_heads; r.capacity = g->recent_capacity; r.page_size = g->page_size;
+  return r;
+}
+
+int check_ring(const R2KGeom* g, const R2KCacheView* v) {
+  if (!v->recent_k || !v->recent_v || !v->recent_len || !v->recent_global || !v->recent_logical || !v->recent_page_lengths)
+    return R2K_ERR_NULL;
+  if (!aligned16(v->recent_k) || !aligned16(v->recent_v) || (v->recent_k_bstride & 15) || (v->recent_v_bstride & 15))
+    return R2K_ERR_ALIGNMENT;
+  if ((v->recent_len_bstride & 3) || (v->recent_global_bstride & 7) || (v->recent_logical_bstride & 7) ||
+      (v->recent_page_lengths_bstride & 7))
+    return R2K_ERR_ALIGNMENT;
+  (void)g;
+  return R2K_OK;
+}
+
+}  // namespace
+}  // namespace r2k
+
+using namespace r2k;
+
+extern "C" {
+
+const char* r2k_status_string(int status) {
+  switch (status) {
+    case R2K_OK: return "ok";
+    case R2K_ERR_NULL: return "required pointer is NULL";
+    case R2K_ERR_GEOMETRY: return "unsupported or inconsistent geometry";
+    case R2K_ERR_ALIGNMENT: return "pointer or stride is not sufficiently aligned";
+    case R2K_ERR_CAPACITY: return "capacity exhausted";
+    case R2K_ERR_WORKSPACE: return "workspace too small";
+    case R2K_ERR_CUDA: return "CUDA runtime error";
+    case R2K_ERR_DEVICE_TIMEOUT: return "bounded device-side wait timed out";
+    case R2K_ERR_EMPTY: return "cache holds no tokens";
+    default: return "unknown status";
+  }
+}
+
+uint64_t r2k_launch_count(void) { return g_launches.load(); }
+
+int r2k_decode_workspace_bytes(const R2KGeom* geom, size_t* bytes) {
+  if (bytes == nullptr) return R2K_ERR_NULL;
+  int rc = check_geom(geom);
+  if (rc) return rc;
+  DecodeParams p;
+  rc = derive(geom, &p);
+  if (rc) return rc;
+  *bytes = kWsHeaderBytes + counters_bytes(p) + (size_t)p.bh_total * p.parts_cap * kSlotFloats * sizeof(float);
+  return R2K_OK;
+}
+
+int r2k_decode_workspace_init(void* workspace, size_t bytes, void* stream) {
+  if (workspace == nullptr) return R2K_ERR_NULL;
+  if (bytes < (size_t)kWsHeaderBytes) return R2K_ERR_WORKSPACE;
+  // header + counters: clear everything in front of the partial slots that this workspace could ever hold
+  size_t n = bytes < (size_t)(1 << 20) ? bytes : (size_t)(1 << 20);
+  return cudaMemsetAsync(workspace, 0, n, reinterpret_cast<cudaStream_t>(stream)) == cudaSuccess ? R2K_OK : R2K_ERR_CUDA;
+}
+
+int r2k_decode(const R2KGeom* geom, const R2KCacheView* view, const void* q, const R2KAppend* append, void* workspace,
+               size_t workspace_bytes, void* out, uint32_t flags, void* stream) {
+  if (view == nullptr || q == nullptr || workspace == nullptr || out == nullptr) return R2K_ERR_NULL;
+  int rc = check_geom(geom);
+  if (rc) return rc;
+  DecodeParams p;
+  rc = derive(geom, &p);
+  if (rc) return rc;
+  const size_t need = kWsHeaderBytes + counters_bytes(p) + (size_t)p.bh_total * p.parts_cap * kSlotFloats * sizeof(float);
+  if (workspace_bytes < need) return R2K_ERR_WORKSPACE;
+  if (!aligned16(workspace) || !aligned16(q) || !aligned16(out)) return R2K_ERR_ALIGNMENT;
+  const bool need_k = geom->n_fp + geom->n_i4 + geom->n_i2 > 0;
+  if (need_k && (!view->k_packed || !view->k_scale || !view->k_zero)) return R2K_ERR_NULL;
+  if (geom->n_fp && !view->fp_v) return R2K_ERR_NULL;
+  if (geom->n_i4 && (!view->i4_packed || !view->i4_scale)) return R2K_ERR_NULL;
+  if (geom->n_i2 && (!view->i2_packed || !view->i2_scale || !view->i2_zero)) return R2K_ERR_NULL;
+  if (geom->recent_capacity > 0) {
+    rc = check_ring(geom, view);
+    if (rc) return rc;
+  } else if (!view->recent_len) {
+    return R2K_ERR_NULL;
+  }
+  if (!aligned16(view->k_packed) || !aligned16(view->k_scale) || !aligned16(view->k_zero) || !aligned16(view->fp_v) ||
+      !aligned16(view->i4_packed) || !aligned16(view->i2_packed))
+    return R2K_ERR_ALIGNMENT;
+  if ((view->k_packed_bstride | view->k_scale_bstride | view->k_zero_bstride | view->fp_v_bstride | view->i4_packed_bstride |
+       view->i2_packed_bstride) & 15)
+    return R2K_ERR_ALIGNMENT;
+  p.v = *view;
+  p.q = q;
+  if (append != nullptr && append->k != nullptr) {
+    if (append->v == nullptr) return R2K_ERR_NULL;
+    if (geom->recent_capacity <= 0) return R2K_ERR_CAPACITY;
+    if (!aligned16(append->k) || !aligned16(append->v)) return R2K_ERR_ALIGNMENT;
+    p.app_k = append->k; p.app_v = append->v; p.app_idx = append->indices;
+    p.app_global = append->global_index; p.app_logical = append->logical_position;
+  }
+  p.out = out;
+  p.flags = flags;
+  uint8_t* ws = reinterpret_cast<uint8_t*>(workspace);
+  p.err = reinterpret_cast<int*>(ws);
+  p.bh_counter = reinterpret_cast<int*>(ws + kWsHeaderBytes);
+  p.req_counter = p.bh_counter + p.bh_total;
+  p.partials = reinterpret_cast<float*>(ws + kWsHeaderBytes + counters_bytes(p));
+
+  DeviceInfo* dev;
+  rc = device_info(&dev);
+  if (rc) return rc;
+  if (!dev->attr_set) {
+    if (cudaFuncSetAttribute(decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess ||
+        cudaFuncSetAttribute(decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+      return R2K_ERR_CUDA;
+    cudaFuncSetAttribute(decode_kernel<true>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    cudaFuncSetAttribute(decode_kernel<false>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    dev->attr_set = true;
+  }
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (geom->dtype == R2K_DTYPE_BF16)
+    decode_kernel<true><<<p.grid, kThreads, kSmemBytes, st>>>(p);
+  else
+    decode_kernel<false><<<p.grid, kThreads, kSmemBytes, st>>>(p);
+  ++g_launches;
+  return cudaGetLastError() == cudaSuccess ? R2K_OK : R2K_ERR_CUDA;
+}
+
+int r2k_decode_device_status(void* workspace, int32_t* status, void* stream) {
+  if (workspace == nullptr || status == nullptr) return R2K_ERR_NULL;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (cudaMemcpyAsync(status, workspace, sizeof(int32_t), cudaMemcpyDeviceToHost, st) != cudaSuccess) return R2K_ERR_CUDA;
+  return cudaStreamSynchronize(st) == cudaSuccess ? R2K_OK : R2K_ERR_CUDA;
+}
+
+int r2k_merge_states(const float* states, int32_t num_states, int64_t state_stride, int32_t rows, int32_t dtype, void* out,
+                     uint32_t flags, void* stream) {
+  if (states == nullptr || out == nullptr) return R2K_ERR_NULL;
+  if (num_states < 1 || rows < 1 || (dtype != R2K_DTYPE_BF16 && dtype != R2K_DTYPE_FP16)) return R2K_ERR_GEOMETRY;
+  if ((reinterpret_cast<uintptr_t>(states) & 7u) || (state_stride & 1) || !aligned16(out)) return R2K_ERR_ALIGNMENT;
+  merge_states_kernel<<<(rows + 3) / 4, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(states, num_states, state_stride, rows,
+                                                                                         dtype, out, flags);
+  ++g_launches;
+  return cudaGetLastError() == cudaSuccess ? R2K_OK : R2K_ERR_CUDA;
+}
+
+static int check_pack(const void* src, int32_t dtype, int32_t heads, int64_t src_rows, int64_t count, int64_t capacity,
+                      int64_t dst_start) {
+  if (src == nullptr) return R2K_ERR_NULL;
+  if (dtype != R2K_DTYPE_BF16 && dtype != R2K_DTYPE_FP16) return R2K_ERR_GEOMETRY;
+  if (heads < 1 || src_rows < 0 || count < 0 || dst_start < 0) return R2K_ERR_GEOMETRY;
+  if (dst_start + count > capacity) return R2K_ERR_CAPACITY;
+  if (reinterpret_cast<uintptr_t>(src) & 7u) return R2K_ERR_ALIGNMENT;
+  return R2K_OK;
+}
+
+int r2k_pack_k_int4(const void* src, int32_t dtype, int32_t num_kv_heads, int64_t src_rows, const int64_t* index, int64_t count,
+                    uint8_t* k_packed, void* k_scale, uint8_t* k_zero, int64_t k_capacity, int32_t k_block, int64_t dst_start,
+                    void* stream) {
+  int rc = check_pack(src, dtype, num_kv_heads, src_rows, count, k_capacity, dst_start);
+  if (rc) return rc;
+  if (!k_packed || !k_scale || !k_zero) return R2K_ERR_NULL;
+  if (!pow2_in(k_block, 32, 64, 128) || k_capacity % k_block) return R2K_ERR_GEOMETRY;
+  if (count == 0) return R2K_OK;
+  PackArgs a{reinterpret_cast<const uint16_t*>(src), 0, src_rows, index, count, k_capacity, dst_start, num_kv_heads};
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  return dtype == R2K_DTYPE_BF16 ? launch_pack_k<true>(a, 1, k_packed, k_scale, k_zero, 0, 0, 0, k_block, st)
+                                 : launch_pack_k<false>(a, 1, k_packed, k_scale, k_zero, 0, 0, 0, k_block, st);
+}
+
+int r2k_pack_v_int4(const void* src, int32_t dtype, int32_t num_kv_heads, int64_t src_rows, const int64_t* index, int64_t count,
+                    uint8_t* packed, float* scale, int64_t capacity, int64_t dst_start, void* stream) {
+  int rc = check_pack(src, dtype, num_kv_heads, src_rows, count, capacity, dst_start);
+  if (rc) return rc;
+  if (!packed || !scale) return R2K_ERR_NULL;
+  if (count == 0) return R2K_OK;
+  PackArgs a{reinterpret_cast<const uint16_t*>(src), 0, src_rows, index, count, capacity, dst_start, num_kv_heads};
+  dim3 grid((unsigned)((count + 3) / 4), (unsigned)num_kv_heads, 1);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == R2K_DTYPE_BF16) pack_v_int4_kernel<true><<<grid, 128, 0, st>>>(a, packed, scale, 0, 0);
+  else pack_v_int4_kernel<false><<<grid, 128, 0, st>>>(a, packed, scale, 0, 0);
+  ++g_launches;
+  return cudaGetLastError() == cudaSuccess ? R2K_OK : R2K_ERR_CUDA;
+}
+
+int r2k_pack_v_int2(const void* src, int32_t dtype, int32_t num_kv_heads, int64_t src_rows, const int64_t* index, int64_t count,
+                    uint8_t* packed, void* scale, uint8_t* zero, int64_t capacity, int32_t group, int64_t dst_start, void* stream) {
+  int rc = check_pack(src, dtype, num_kv_heads, src_rows, count, capacity, dst_start);
+  if (rc) return rc;
+  if (!packed || !scale || !zero) return R2K_ERR_NULL;
+  if (!pow2_in(group, 32, 64, 128)) return R2K_ERR_GEOMETRY;
+  if (count == 0) return R2K_OK;
+  PackArgs a{reinterpret_cast<const uint16_t*>(src), 0, src_rows, index, count, capacity, dst_start, num_kv_heads};
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  return dtype == R2K_DTYPE_BF16 ? launch_pack_v2<true>(a, 1, packed, scale, zero, 0, 0, 0, group, st)
+                                 : launch_pack_v2<false>(a, 1, packed, scale, zero, 0, 0, 0, group, st);
+}
+
+int r2k_gather_rows(const void* src, int32_t num_kv_heads, int64_t src_rows, const int64_t* index, int64_t count, void* dst,
+                    int64_t dst_rows, int64_t dst_start, void* stream) {
+  if (src == nullptr || dst == nullptr) return R2K_ERR_NULL;
+  if (num_kv_heads < 1 || count < 0 || dst_start < 0) return R2K_ERR_GEOMETRY;
+  if (dst_start + count > dst_rows) return R2K_ERR_CAPACITY;
+  if ((reinterpret_cast<uintptr_t>(src) | reinterpret_cast<uintptr_t>(dst)) & 7u) return R2K_ERR_ALIGNMENT;
+  if (count == 0) return R2K_OK;
+  dim3 grid((unsigned)((count + 3) / 4), (unsigned)num_kv_heads, 1);
+  gather_rows_kernel<<<grid, 128, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      reinterpret_cast<const uint16_t*>(src), src_rows, index, count, reinterpret_cast<uint16_t*>(dst), dst_rows, dst_start);
+  ++g_launches;
+  return cudaGetLastError() == cudaSuccess ? R2K_OK : R2K_ERR_CUDA;
+}
+
+int r2k_append_recent(const R2KGeom* geom, const R2KCacheView* view, const R2KAppend* append, void* stream) {
+  if (view == nullptr || append == nullptr || append->k == nullptr || append->v == nullptr) return R2K_ERR_NULL;
+  int rc = check_geom(geom);
+  if (rc) return rc;
+  if (geom->recent_capacity <= 0) return R2K_ERR_CAPACITY;
+  rc = check_ring(geom, view);
+  if (rc) return rc;
+  if (!aligned16(append->k) || !aligned16(append->v)) return R2K_ERR_ALIGNMENT;
+  append_recent_kernel<<<geom->batch, 256, 0, reinterpret_cast<cudaStream_t>(stream)>>>(
+      ring_args(geom, view), reinterpret_cast<const uint8_t*>(append->k), reinterpret_cast<const uint8_t*>(append->v),
+      append->indices, append->global_index, append->logical_position);
+  ++g_launches;
+  return cudaGetLastError() == cudaSuccess ? R2K_OK : R2K_ERR_CUDA;
+}
+
+int r2k_flush_recent(const R2KGeom* geom, const R2KCacheView* view, int32_t ring_tokens, int32_t flush_tokens, int64_t k_dst,
+                     int64_t v_dst, int64_t* i2_global, int64_t* i2_logical, int64_t meta_bstride, int64_t v_meta_dst,
+                     void* stream) {
+  if (view == nullptr) return R2K_ERR_NULL;
+  int rc = check_geom(geom);
+  if (rc) return rc;
+  rc = check_ring(geom, view);
+  if (rc) return rc;
+  if (flush_tokens < 1 || ring_tokens < flush_tokens || ring_tokens > geom->recent_capacity) return R2K_ERR_GEOMETRY;
+  if (k_dst < 0 || v_dst < 0 || k_dst + flush_tokens > geom->k_capacity || v_dst + flush_tokens > geom->i2_capacity)
+    return R2K_ERR_CAPACITY;
+  if (!view->k_packed || !view->k_scale || !view->k_zero || !view->i2_packed || !view->i2_scale || !view->i2_zero)
+    return R2K_ERR_NULL;
+  if ((i2_global == nullptr) != (i2_logical == nullptr)) return R2K_ERR_NULL;
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  const bool bf16 = geom->dtype == R2K_DTYPE_BF16;
+  PackArgs ka{reinterpret_cast<const uint16_t*>(view->recent_k), view->recent_k_bstride, geom->recent_capacity, nullptr,
+              flush_tokens, geom->k_capacity, k_dst, geom->num_kv_heads};
+  uint8_t* kp = const_cast<uint8_t*>(view->k_packed);
+  void* ks = const_cast<void*>(view->k_scale);
+  uint8_t* kz = const_cast<uint8_t*>(view->k_zero);
+  rc = bf16 ? launch_pack_k<true>(ka, geom->batch, kp, ks, kz, view->k_packed_bstride, view->k_scale_bstride, view->k_zero_bstride,
+                                  geom->k_block, st)
+            : launch_pack_k<false>(ka, geom->batch, kp, ks, kz, view->k_packed_bstride, view->k_scale_bstride, view->k_zero_bstride,
+                                   geom->k_block, st);
+  if (rc) return rc;
+  PackArgs va{reinterpret_cast<const uint16_t*>(view->recent_v), view->recent_v_bstride, geom->recent_capacity, nullptr,
+              flush_tokens, geom->i2_capacity, v_dst, geom->num_kv_heads};
+  uint8_t* vp = const_cast<uint8_t*>(view->i2_packed);
+  void* vs = const_cast<void*>(view->i2_scale);
+  uint8_t* vz = const_cast<uint8_t*>(view->i2_zero);
+  rc = bf16 ? launch_pack_v2<true>(va, geom->batch, vp, vs, vz, view->i2_packed_bstride, view->i2_scale_bstride,
+                                   view->i2_zero_bstride, geom->v2_group, st)
+            : launch_pack_v2<false>(va, geom->batch, vp, vs, vz, view->i2_packed_bstride, view->i2_scale_bstride,
+                                    view->i2_zero_bstride, geom->v2_group, st);
+  if (rc) return rc;
+  flush_ring_kernel<<<geom->batch, 256, 0, st>>>(ring_args(geom, view), ring_tokens, flush_tokens, i2_global, i2_logical,
+                                                 meta_bstride, v_meta_dst);
+  ++g_launches;
+  return cudaGetLastError() == cudaSuccess ? R2K_OK : R2K_ERR_CUDA;
+}
+
+}  // extern "C"
