@@ -112,6 +112,8 @@ class SplitKExecutor:
         self.sm_scale = float(sm_scale)
         self._append = L.Append()
         self._lib = L.lib()
+        self._geom = arenas.geom(self.num_query_heads, sm_scale=self.sm_scale)
+        self._idx = None
 
     @property
     def batched(self) -> bool:
@@ -119,7 +121,8 @@ class SplitKExecutor:
 
     def _launch(self, query, append, out_ptr, flags) -> None:
         a = self.arenas
-        geom = a.geom(self.num_query_heads, sm_scale=self.sm_scale)
+        geom = self._geom
+        geom.n_i2 = a.i2_active   # the only extent that moves during generation (flushes)
         ws = self.workspace.buffer
         L.check(self._lib.r2k_decode(
             C.byref(geom), C.byref(a.view()), C.c_void_p(query.data_ptr()), append,
