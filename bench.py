@@ -141,10 +141,10 @@ def build_batched_executor(batch, tokens, seed, device, p_fp=0.25, p_i4=0.5):
 class ReplicaBench:
     """Round-robin over `sets` batched caches; decode+append every step, flush every 128 steps per set."""
 
-    def __init__(self, device, batch=8, tokens=32768, sets=4):
+    def __init__(self, device, batch=8, tokens=32768, sets=4, p_fp=0.25, p_i4=0.5):
         import r2omni_b200 as R
         self.R, self.device, self.batch, self.tokens = R, device, batch, tokens
-        self.ex = [build_batched_executor(batch, tokens, 11 + s, device) for s in range(sets)]
+        self.ex = [build_batched_executor(batch, tokens, 11 + s, device, p_fp, p_i4) for s in range(sets)]
         g = torch.Generator(device=device).manual_seed(5)
         self.q = torch.randn(batch, HQ, D, generator=g, device=device).to(torch.bfloat16)
         self.k = torch.randn(batch, HKV, D, generator=g, device=device).to(torch.bfloat16)
@@ -391,6 +391,7 @@ def main():
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sharded", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
+    ap.add_argument("--page-mix", default="25,50,25", help="percent of bf16,INT4,INT2 value pages (kernel studies)")
     args = ap.parse_args()
     if args.impl == "reference":
         run_reference_arm(args)
@@ -409,7 +410,8 @@ def main():
 
     warmup = max(args.warmup, 3)
     tokens, batch = (32768, 8) if args.workload == "decode_32k_b8" else (4096, 2)
-    bench = ReplicaBench(device, batch=batch, tokens=tokens, sets=4)
+    mix = [float(x) / 100.0 for x in args.page_mix.split(",")]
+    bench = ReplicaBench(device, batch=batch, tokens=tokens, sets=4, p_fp=mix[0], p_i4=mix[1])
     bench.run_graph_steps(warmup)
     launches0 = L.lib().r2k_launch_count()
     with ClockSampler(local) as clocks:
@@ -470,7 +472,7 @@ def main():
             "scaling": "weak", "vs_baseline": None, "dtype": "f16 tensor-core products, f32 accumulation (u4/u2 codes, bf16 pages)",
             "data": "synthetic",
             "config": {"workload": args.workload, "batch_per_gpu": batch, "tokens_per_request": tokens, "heads": "16q/2kv x128",
-                       "pages": "64 tokens; bf16/INT4/INT2 = 25/50/25 % from a seed", "keys": "INT4 per channel, 32-token blocks",
+                       "pages": f"64 tokens; bf16/INT4/INT2 = {args.page_mix} % from a seed", "keys": "INT4 per channel, 32-token blocks",
                        "residual_window": RING, "append_per_step": 1, "flush_every": RING,
                        "l2": "4 cache sets of ~98 MB visited round-robin (inputs larger than L2)",
                        "parallelism": f"{world} independent replicas" if world > 1 else "1 GPU",

@@ -53,38 +53,57 @@ struct DecodeParams {
   int* err;
   int* bh_counter;
   int* req_counter;
+  int* group_counter;
   float* partials;
-  int parts_cap;
+  float* group_partials;
+  int parts_cap, groups_cap;
   // derived
   int gqa, bh_total, grid;
   int nF, n4, n2, nR, units;      // tiles per (request, kv head) and their sum
   int wF0, w40, w20;              // arena row of the first window of each pool
-  int64_t cF, c4, c2, cR, c_bh, c_total;
+  uint32_t cF, c4, c2, cR, c_bh;  // tile cost weights and their sum per (request, kv head); c_bh < 2^22
   int groups2, group2_shift, kblock_shift;
   float qscale;                   // sm_scale * log2(e)
 };
 
+// Work is laid out on a cost axis: (request, kv head) bh owns [bh*c_bh, (bh+1)*c_bh), a tile owns its cost
+// weight inside it.  CTA i owns [pos(i), pos(i+1)) with pos(i) = ceil(i * BH * c_bh / grid), kept as a
+// (bh, remainder) pair so that everything stays in 32-bit arithmetic.
+struct CostPos {
+  int bh;
+  uint32_t r;
+};
+__host__ __device__ inline CostPos cta_pos(const DecodeParams& p, int i) {
+  const uint32_t a = (uint32_t)i * (uint32_t)p.bh_total, g = (uint32_t)p.grid;
+  CostPos c;
+  c.bh = (int)(a / g);
+  c.r = ((a % g) * p.c_bh + g - 1) / g;
+  if (c.r >= p.c_bh) { c.bh += 1; c.r = 0; }
+  return c;
+}
 // Number of tiles of one (request, kv head) whose cost coordinate starts before r.
-__host__ __device__ inline int units_before(const DecodeParams& p, int64_t r) {
+__host__ __device__ inline int units_before(const DecodeParams& p, uint32_t r) {
   int n = 0;
-  const int cnt[4] = {p.nF, p.n4, p.n2, p.nR};
-  const int64_t cost[4] = {p.cF, p.c4, p.c2, p.cR};
+  const uint32_t cnt[4] = {(uint32_t)p.nF, (uint32_t)p.n4, (uint32_t)p.n2, (uint32_t)p.nR};
+  const uint32_t cost[4] = {p.cF, p.c4, p.c2, p.cR};
+#pragma unroll
   for (int k = 0; k < 4; ++k) {
-    if (r <= 0) return n;
-    int64_t a = (r + cost[k] - 1) / cost[k];
-    n += a < cnt[k] ? (int)a : cnt[k];
-    r -= (int64_t)cnt[k] * cost[k];
+    if (r == 0) return n;
+    const uint32_t span = cnt[k] * cost[k];
+    if (r >= span) { n += (int)cnt[k]; r -= span; }
+    else { n += (int)((r + cost[k] - 1) / cost[k]); return n; }
   }
   return n;
 }
-__host__ __device__ inline int64_t cta_cost_begin(const DecodeParams& p, int i) {
-  return ((int64_t)i * p.c_total + p.grid - 1) / p.grid;
-}
+// First and last CTA whose cost interval intersects bh's (a CTA with an empty interval strictly inside counts).
 __host__ __device__ inline int first_cta_of(const DecodeParams& p, int bh) {
-  return (int)(((int64_t)bh * p.c_bh * p.grid) / p.c_total);
+  return (int)(((uint32_t)bh * (uint32_t)p.grid) / (uint32_t)p.bh_total);
 }
 __host__ __device__ inline int last_cta_of(const DecodeParams& p, int bh) {
-  return (int)(((((int64_t)bh + 1) * p.c_bh - 1) * p.grid) / p.c_total);
+  int i = (int)((((uint32_t)bh + 1u) * (uint32_t)p.grid) / (uint32_t)p.bh_total);
+  if (i > p.grid - 1) i = p.grid - 1;
+  while (i > 0 && cta_pos(p, i).bh > bh) --i;
+  return i;
 }
 
 }  // namespace r2k

@@ -66,12 +66,10 @@ __device__ __forceinline__ Tile tile_of(const DecodeParams& p, int u) {
   return t;
 }
 
-// The unit range [u0,u1) of (request,kv head) `bh` owned by CTA `cta`.
-__device__ __forceinline__ void unit_range(const DecodeParams& p, int cta, int bh, int& u0, int& u1) {
-  const int64_t base = (int64_t)bh * p.c_bh;
-  int64_t lo = cta_cost_begin(p, cta) - base, hi = cta_cost_begin(p, cta + 1) - base;
-  lo = lo < 0 ? 0 : lo;
-  hi = hi > p.c_bh ? p.c_bh : hi;
+// The unit range [u0,u1) of (request,kv head) `bh` inside a CTA's cost interval [c0, c1).
+__device__ __forceinline__ void unit_range(const DecodeParams& p, const CostPos& c0, const CostPos& c1, int bh, int& u0, int& u1) {
+  const uint32_t lo = bh == c0.bh ? c0.r : 0u;
+  const uint32_t hi = bh == c1.bh ? c1.r : p.c_bh;
   u0 = units_before(p, lo);
   u1 = units_before(p, hi);
 }
@@ -129,8 +127,10 @@ __device__ __forceinline__ void softmax_update(WarpState& st, float (&s)[NT][4])
     mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, d));
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, d));
   }
+  // Lazy reference point: the running "max" only moves when a score exceeds it by more than 2^8, so
+  // probabilities stay below 256 (exact enough in fp16/fp32) and most blocks skip the rescale.
   const float n0 = fmaxf(st.m[0], mx0), n1 = fmaxf(st.m[1], mx1);
-  if (__any_sync(0xffffffffu, (n0 > st.m[0]) | (n1 > st.m[1]))) {
+  if (__any_sync(0xffffffffu, (mx0 > st.m[0] + 8.f) | (mx1 > st.m[1] + 8.f))) {
     const float f0 = ex2_approx(st.m[0] - n0), f1 = ex2_approx(st.m[1] - n1);  // m = -inf -> 0
     st.l[0] *= f0; st.l[1] *= f1; st.lp[0] *= f0; st.lp[1] *= f1;
 #pragma unroll
@@ -168,8 +168,9 @@ __device__ __forceinline__ void qk_int4(const uint8_t* krows, const uint8_t* ks,
     }
   }
   // zero-point term sum_c Q'[c] * zero[c], as one more MMA chain whose 16 rows are all the zero row
-  float zc[4] = {0.f, 0.f, 0.f, 0.f};
+  float zc[4];
   {
+    float zq[4][4];
     const uint4 za = *reinterpret_cast<const uint4*>(kz + 32 * t);
     const uint4 zb = *reinterpret_cast<const uint4*>(kz + 32 * t + 16);
     const uint32_t z[8] = {za.x, za.y, za.z, za.w, zb.x, zb.y, zb.z, zb.w};
@@ -179,11 +180,14 @@ __device__ __forceinline__ void qk_int4(const uint8_t* krows, const uint8_t* ks,
       const uint32_t y = __byte_perm(z[2 * i], z[2 * i + 1], 0x7632);  // z2 z3 z6 z7
       const uint32_t r0 = x & 0x00FF00FFu, r1 = __byte_perm(x, 0u, 0x4341);
       const uint32_t r2 = y & 0x00FF00FFu, r3 = __byte_perm(y, 0u, 0x4341);
-      mma_f16(zc, r0, r0, r2, r2, qp[4 * i + 0], qp[4 * i + 2]);
-      mma_f16(zc, r1, r1, r3, r3, qp[4 * i + 1], qp[4 * i + 3]);
-      mma_f16(zc, r0, r0, r2, r2, ql[4 * i + 0], ql[4 * i + 2]);
-      mma_f16(zc, r1, r1, r3, r3, ql[4 * i + 1], ql[4 * i + 3]);
+      zq[i][0] = zq[i][1] = zq[i][2] = zq[i][3] = 0.f;   // four independent chains
+      mma_f16(zq[i], r0, r0, r2, r2, qp[4 * i + 0], qp[4 * i + 2]);
+      mma_f16(zq[i], r1, r1, r3, r3, qp[4 * i + 1], qp[4 * i + 3]);
+      mma_f16(zq[i], r0, r0, r2, r2, ql[4 * i + 0], ql[4 * i + 2]);
+      mma_f16(zq[i], r1, r1, r3, r3, ql[4 * i + 1], ql[4 * i + 3]);
     }
+#pragma unroll
+    for (int c = 0; c < 4; ++c) zc[c] = (zq[0][c] + zq[1][c]) + (zq[2][c] + zq[3][c]);
   }
   const float f24 = k2p24 * alpha, f20 = k2p20 * alpha;
 #pragma unroll
@@ -431,7 +435,155 @@ __device__ __forceinline__ void produce_tile(const DecodeParams& p, const Tile& 
   if (lane == 0) mbar_arrive_expect_tx(bar, tx);
 }
 
+// Per-(request, kv head) source bases, biased so that a key-arena row index addresses every array of its pool.
+struct TileSources {
+  const uint8_t* kp; const uint8_t* ks; const uint8_t* kz;
+  const uint8_t* v0; const uint8_t* v1; const uint8_t* v2;   // value payload of pools 0..2
+  const uint8_t* s1;       // INT4-value scales
+  const uint8_t* s2;       // INT2-value scales
+  const uint8_t* z2;       // INT2-value zero points
+  bool fast0, fast1, fast2; // every full tile of the pool can go through 16-byte-aligned bulk copies
+};
+
+__device__ __forceinline__ TileSources tile_sources(const DecodeParams& p, int b, int h) {
+  const R2KCacheView& v = p.v;
+  TileSources s;
+  const int64_t hb = h;
+  s.kp = v.k_packed + (int64_t)b * v.k_packed_bstride + hb * p.g.k_capacity * 64;
+  s.ks = (const uint8_t*)v.k_scale + (int64_t)b * v.k_scale_bstride + hb * (p.g.k_capacity >> p.kblock_shift) * 256;
+  s.kz = v.k_zero + (int64_t)b * v.k_zero_bstride + hb * (p.g.k_capacity >> p.kblock_shift) * 128;
+  const int64_t r0 = hb * p.g.fp_capacity - p.g.k_off_fp, r1 = hb * p.g.i4_capacity - p.g.k_off_i4,
+                r2 = hb * p.g.i2_capacity - p.g.k_off_i2;
+  s.v0 = (const uint8_t*)v.fp_v + (int64_t)b * v.fp_v_bstride + r0 * 256;
+  s.v1 = v.i4_packed + (int64_t)b * v.i4_packed_bstride + r1 * 64;
+  s.v2 = v.i2_packed + (int64_t)b * v.i2_packed_bstride + r2 * 32;
+  s.s1 = (const uint8_t*)v.i4_scale + (int64_t)b * v.i4_scale_bstride + r1 * 4;
+  s.s2 = (const uint8_t*)v.i2_scale + (int64_t)b * v.i2_scale_bstride + r2 * p.groups2 * 2;
+  s.z2 = v.i2_zero + (int64_t)b * v.i2_zero_bstride + r2 * p.groups2;
+  // full tiles start at multiples of 64 rows, so base alignment decides everything
+  s.fast0 = (((uintptr_t)s.v0) & 15) == 0;
+  s.fast1 = ((((uintptr_t)s.v1) | ((uintptr_t)s.s1)) & 15) == 0;
+  s.fast2 = ((((uintptr_t)s.v2) | ((uintptr_t)s.s2) | ((uintptr_t)s.z2)) & 15) == 0 && p.groups2 == 4;
+  return s;
+}
+
+// A full, aligned tile: one lane issues the bulk copies; no per-lane work, no 64-bit multiplies.
+__device__ __forceinline__ void produce_full_tile(const DecodeParams& p, const TileSources& src, int pool, int win,
+                                                  uint8_t* stage, uint64_t* bar) {
+  const int len = pool == 0 ? kTF : kTQ;
+  const int nblk = max(1, len >> p.kblock_shift);
+  const int blk0 = win >> p.kblock_shift;
+  uint32_t tx = (uint32_t)(len * 64 + nblk * 384);
+  tx += pool == 0 ? (uint32_t)(len * 256) : pool == 1 ? (uint32_t)(len * 68) : (uint32_t)(len * 44);
+  mbar_arrive_expect_tx(bar, tx);
+  bulk_g2s(stage + kOffK, src.kp + (size_t)win * 64, (uint32_t)(len * 64), bar);
+  bulk_g2s(stage + kOffKS, src.ks + (size_t)blk0 * 256, (uint32_t)(nblk * 256), bar);
+  bulk_g2s(stage + kOffKZ, src.kz + (size_t)blk0 * 128, (uint32_t)(nblk * 128), bar);
+  if (pool == 0) {
+    bulk_g2s(stage + kOffV, src.v0 + (size_t)win * 256, (uint32_t)(len * 256), bar);
+  } else if (pool == 1) {
+    bulk_g2s(stage + kOffV, src.v1 + (size_t)win * 64, (uint32_t)(len * 64), bar);
+    bulk_g2s(stage + kOffV + kOffI4Scale, src.s1 + (size_t)win * 4, (uint32_t)(len * 4), bar);
+  } else {
+    bulk_g2s(stage + kOffV, src.v2 + (size_t)win * 32, (uint32_t)(len * 32), bar);
+    bulk_g2s(stage + kOffV + kOffI2Scale, src.s2 + (size_t)win * 8, (uint32_t)(len * 8), bar);
+    bulk_g2s(stage + kOffV + kOffI2Zero, src.z2 + (size_t)win * 4, (uint32_t)(len * 4), bar);
+  }
+}
+
 }  // namespace
+
+// Exact merge of `count` partial rows (max, sum, out[128]) of head hh; this thread owns dims 8*sub .. 8*sub+7.
+// Loads are issued eight rows at a time so that their latencies overlap.
+__device__ __forceinline__ void merge_rows(const float* base, int count, int hh, int sub, float& mx, float& lsum,
+                                           float (&acc)[8]) {
+  float m = -INFINITY;
+  for (int q = sub; q < count; q += 16) m = fmaxf(m, __ldcg(base + (size_t)q * kSlotFloats + hh * kRowFloats));
+#pragma unroll
+  for (int d = 1; d < 16; d <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
+  mx = m;
+  lsum = 0.f;
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+  for (int q0 = 0; q0 < count; q0 += 8) {
+    float2 ml[8];
+    float4 va[8], vb[8];
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const int q = min(q0 + k, count - 1);
+      const float* row = base + (size_t)q * kSlotFloats + hh * kRowFloats;
+      ml[k] = __ldcg(reinterpret_cast<const float2*>(row));
+      va[k] = __ldcg(reinterpret_cast<const float4*>(row + 4 + 8 * sub));
+      vb[k] = __ldcg(reinterpret_cast<const float4*>(row + 8 + 8 * sub));
+    }
+#pragma unroll
+    for (int k = 0; k < 8; ++k) {
+      const float w = (q0 + k < count && ml[k].x != -INFINITY) ? ex2_approx(ml[k].x - mx) : 0.f;
+      acc[0] += w * va[k].x; acc[1] += w * va[k].y; acc[2] += w * va[k].z; acc[3] += w * va[k].w;
+      acc[4] += w * vb[k].x; acc[5] += w * vb[k].y; acc[6] += w * vb[k].z; acc[7] += w * vb[k].w;
+      lsum += w * ml[k].y;
+    }
+  }
+}
+
+__device__ __forceinline__ void store_row(float* slot, int hh, int sub, float mx, float lsum, const float (&acc)[8]) {
+  float* orow = slot + hh * kRowFloats;
+  __stcg(reinterpret_cast<float4*>(orow + 4 + 8 * sub), make_float4(acc[0], acc[1], acc[2], acc[3]));
+  __stcg(reinterpret_cast<float4*>(orow + 8 + 8 * sub), make_float4(acc[4], acc[5], acc[6], acc[7]));
+  if (sub == 0) __stcg(reinterpret_cast<float2*>(orow), make_float2(mx, lsum));
+}
+
+// Normalise (or emit the raw state), optional Hadamard, store.  16 threads per head, 8 dims each.
+template <bool BF16>
+__device__ __forceinline__ void write_output(const DecodeParams& p, size_t orow, bool valid, int sub, float mx, float lsum,
+                                             const float (&acc)[8]) {
+  // every lane takes part in the shuffles below; `valid` only guards the stores (padding heads of GQA < 8)
+  if (p.flags & R2K_FLAG_OUT_STATE) {
+    if (!valid) return;
+    float* o = reinterpret_cast<float*>(p.out) + orow * 130;
+    if (sub == 0) { o[0] = mx * kLn2; o[1] = lsum; }
+#pragma unroll
+    for (int e = 0; e < 8; e += 2) *reinterpret_cast<float2*>(o + 2 + 8 * sub + e) = make_float2(acc[e], acc[e + 1]);
+    return;
+  }
+  const float inv = 1.f / lsum;
+  float r[8];
+#pragma unroll
+  for (int e = 0; e < 8; ++e) r[e] = acc[e] * inv;
+  if (p.flags & R2K_FLAG_OUTPUT_HADAMARD) {
+#pragma unroll
+    for (int e = 0; e < 8; ++e)  // round through the element type first, as the reference does
+      r[e] = BF16 ? __bfloat162float(__float2bfloat16_rn(r[e])) : __half2float(__float2half_rn(r[e]));
+#pragma unroll
+    for (int span = 1; span < 8; span <<= 1) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        if ((e & span) == 0) { const float a = r[e], c = r[e + span]; r[e] = a + c; r[e + span] = a - c; }
+      }
+    }
+#pragma unroll
+    for (int sft = 1; sft < 16; sft <<= 1) {
+#pragma unroll
+      for (int e = 0; e < 8; ++e) {
+        const float o2 = __shfl_xor_sync(0xffffffffu, r[e], sft);
+        r[e] = (sub & sft) ? (o2 - r[e]) : (r[e] + o2);
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) r[e] *= 0.08838834764831845f;
+  }
+  if (!valid) return;
+  if (p.flags & R2K_FLAG_OUT_F32) {
+    float* o = reinterpret_cast<float*>(p.out) + orow * kD + 8 * sub;
+    *reinterpret_cast<float4*>(o) = make_float4(r[0], r[1], r[2], r[3]);
+    *reinterpret_cast<float4*>(o + 4) = make_float4(r[4], r[5], r[6], r[7]);
+  } else {
+    uint4 pk;
+    if (BF16) { pk.x = pack_bf16x2(r[0], r[1]); pk.y = pack_bf16x2(r[2], r[3]); pk.z = pack_bf16x2(r[4], r[5]); pk.w = pack_bf16x2(r[6], r[7]); }
+    else { pk.x = pack_f16x2(r[0], r[1]); pk.y = pack_f16x2(r[2], r[3]); pk.z = pack_f16x2(r[4], r[5]); pk.w = pack_f16x2(r[6], r[7]); }
+    *reinterpret_cast<uint4*>(reinterpret_cast<uint16_t*>(p.out) + orow * kD + 8 * sub) = pk;
+  }
+}
 
 // ---------------------------------------------------------------------------
 // kernel
@@ -453,8 +605,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const __gr
   }
   __syncthreads();
 
-  const int64_t x0 = cta_cost_begin(p, cta), x1 = cta_cost_begin(p, cta + 1);
-  int bh_lo = (int)(x0 / p.c_bh), bh_hi = (int)((x1 - 1) / p.c_bh);
+  const CostPos c0 = cta_pos(p, cta), c1 = cta_pos(p, cta + 1);
+  const int bh_lo = c0.bh;
+  int bh_hi = c1.r > 0 ? c1.bh : c1.bh - 1;
   if (bh_hi > p.bh_total - 1) bh_hi = p.bh_total - 1;
   const bool has_append = p.app_k != nullptr;
 
@@ -467,9 +620,10 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const __gr
     for (int bh = bh_lo; bh <= bh_hi && alive; ++bh) {
       const int b = bh / p.g.num_kv_heads, h = bh - b * p.g.num_kv_heads;
       int u0, u1;
-      unit_range(p, cta, bh, u0, u1);
+      unit_range(p, c0, c1, bh, u0, u1);
       const int rlen = *reinterpret_cast<const int*>((const uint8_t*)p.v.recent_len + (size_t)b * p.v.recent_len_bstride) +
                        (has_append ? 1 : 0);
+      const TileSources src = tile_sources(p, b, h);
       for (int u = u0; u < u1; ++u) {
         const Tile tl = tile_of(p, u);
         if (tl.pool == 3 && tl.win >= rlen) continue;
@@ -478,7 +632,13 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const __gr
           alive = false;
           break;
         }
-        produce_tile(p, tl, b, h, stages + stage * kStageBytes, &full_bar[stage], lane);
+        uint8_t* sb = stages + stage * kStageBytes;
+        const bool full = tl.pool < 3 && tl.lo == 0 && tl.hi == (tl.pool == 0 ? kTF : kTQ) && (tl.pool == 0 ? src.fast0 : tl.pool == 1 ? src.fast1 : src.fast2);
+        if (full) {
+          if (lane == 0) produce_full_tile(p, src, tl.pool, tl.win, sb, &full_bar[stage]);
+        } else {
+          produce_tile(p, tl, b, h, sb, &full_bar[stage], lane);
+        }
         if (++stage == kStages) { stage = 0; phase ^= 1u; }
       }
     }
@@ -493,7 +653,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const __gr
   for (int bh = bh_lo; bh <= bh_hi; ++bh) {
     const int b = bh / p.g.num_kv_heads, h = bh - b * p.g.num_kv_heads;
     int u0, u1;
-    unit_range(p, cta, bh, u0, u1);
+    unit_range(p, c0, c1, bh, u0, u1);
     const int rlen0 = *reinterpret_cast<const int*>((const uint8_t*)p.v.recent_len + (size_t)b * p.v.recent_len_bstride);
     const int rlen = rlen0 + (has_append ? 1 : 0);
     state_reset(st);
@@ -548,16 +708,21 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const __gr
             }
           }
         } else if (tl.pool == 0) {
-          const int r0 = 16 * warp;
-          const int lo = max(tl.lo - r0, 0), hi = min(tl.hi - r0, 16);
-          if (hi > lo) {
-            const int blk = ((tl.win + r0) >> p.kblock_shift) - (tl.win >> p.kblock_shift);
-            float s[1][4];
-            qk_int4<1>(sb + kOffK + r0 * 64, sb + kOffKS + blk * 256, sb + kOffKZ + blk * 128, qh, t, pg, p.qscale, s);
-            if ((lo > 0) | (hi < 16)) mask_scores(s[0], pg, lo, hi);
-            softmax_update<1>(st, s);
-            set_units(st, 0);
-            pv_fp<BF16>(st, sb + kOffV + r0 * 256, s[0], g, t);
+          // 64-token tile = two key blocks: warps {0,1} take even tiles, {2,3} odd ones, 32 tokens per warp,
+          // so the per-block work (Q' and zero-point chain) is paid once per 32 tokens here as well
+          if (((u ^ (warp >> 1)) & 1) == 0) {
+            const int r0 = 32 * (warp & 1);
+            const int lo = max(tl.lo - r0, 0), hi = min(tl.hi - r0, 32);
+            if (hi > lo) {
+              const int blk = ((tl.win + r0) >> p.kblock_shift) - (tl.win >> p.kblock_shift);
+              float s[2][4];
+              qk_int4<2>(sb + kOffK + r0 * 64, sb + kOffKS + blk * 256, sb + kOffKZ + blk * 128, qh, t, pg, p.qscale, s);
+              if ((lo > 0) | (hi < 32)) { mask_scores(s[0], pg, lo, hi); mask_scores(s[1], 16 + pg, lo, hi); }
+              softmax_update<2>(st, s);
+              set_units(st, 0);
+#pragma unroll
+              for (int j = 0; j < 2; ++j) pv_fp<BF16>(st, sb + kOffV + (r0 + 16 * j) * 256, s[j], g, t);
+            }
           }
         } else if (warp < 2) {
           const int r0 = 16 * warp;
@@ -633,67 +798,43 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const __gr
       __stcg(reinterpret_cast<float4*>(orow + 8 + 8 * sub), a1);
       if (sub == 0) __stcg(reinterpret_cast<float2*>(orow), make_float2(mx, lsum));
     }
-    __threadfence();
+    // ---- two-level exact merge: groups of 32 partials, then the group results ----
+    // Release pattern: the CTA barrier orders every thread's partial stores before thread 0's fence, whose
+    // cumulativity publishes them before the ticket; the reader side mirrors it (ticket, fence, barrier).
+    const int hh = threadIdx.x >> 4, sub = threadIdx.x & 15;
+    const int part = cta - part0, grp = part >> 5, ngroups = (nparts + 31) >> 5;
+    const int gsize = min(32, nparts - 32 * grp);
+    float mx, lsum, acc[8];
     named_bar_sync(1, kConsumers);
     if (threadIdx.x == 0) {
-      const int ticket = atomicAdd(&p.bh_counter[bh], 1);
-      flags[0] = (ticket == nparts - 1);
+      __threadfence();
+      const int ticket = atomicAdd(&p.group_counter[bh * p.groups_cap + grp], 1);
+      flags[0] = (ticket == gsize - 1);
+      if (flags[0]) p.group_counter[bh * p.groups_cap + grp] = 0;
       __threadfence();
     }
     named_bar_sync(1, kConsumers);
-    if (flags[0]) {
-      // ---- last arriver: exact merge of all partials of (b, h), epilogue, fused append ----
-      const float* base = p.partials + (size_t)bh * p.parts_cap * kSlotFloats;
-      for (int hh = warp; hh < p.gqa; hh += kNW) {
-        float mx = -INFINITY;
-        for (int q = lane; q < nparts; q += 32) mx = fmaxf(mx, __ldcg(base + (size_t)q * kSlotFloats + hh * kRowFloats));
-#pragma unroll
-        for (int d = 1; d < 32; d <<= 1) mx = fmaxf(mx, __shfl_xor_sync(0xffffffffu, mx, d));
-        float4 acc = make_float4(0.f, 0.f, 0.f, 0.f);
-        float lsum = 0.f;
-        for (int q = 0; q < nparts; ++q) {
-          const float* row = base + (size_t)q * kSlotFloats + hh * kRowFloats;
-          const float2 ml = __ldcg(reinterpret_cast<const float2*>(row));
-          const float wgt = (ml.x == -INFINITY) ? 0.f : ex2_approx(ml.x - mx);
-          const float4 v = __ldcg(reinterpret_cast<const float4*>(row + 4 + 4 * lane));
-          acc.x += wgt * v.x; acc.y += wgt * v.y; acc.z += wgt * v.z; acc.w += wgt * v.w;
-          lsum += wgt * ml.y;
+    bool last = flags[0] != 0;
+    if (last) {
+      merge_rows(p.partials + ((size_t)bh * p.parts_cap + 32 * grp) * kSlotFloats, gsize, hh, sub, mx, lsum, acc);
+      if (ngroups > 1) {
+        store_row(p.group_partials + ((size_t)bh * p.groups_cap + grp) * kSlotFloats, hh, sub, mx, lsum, acc);
+        named_bar_sync(1, kConsumers);
+        if (threadIdx.x == 0) {
+          __threadfence();
+          const int ticket = atomicAdd(&p.bh_counter[bh], 1);
+          flags[1] = (ticket == ngroups - 1);
+          if (flags[1]) p.bh_counter[bh] = 0;
+          __threadfence();
         }
-        const size_t orow = (size_t)b * p.g.num_q_heads + h * p.gqa + hh;
-        if (p.flags & R2K_FLAG_OUT_STATE) {
-          float* o = reinterpret_cast<float*>(p.out) + orow * 130;
-          if (lane == 0) { o[0] = mx * kLn2; o[1] = lsum; }
-          o[2 + 4 * lane + 0] = acc.x; o[2 + 4 * lane + 1] = acc.y; o[2 + 4 * lane + 2] = acc.z; o[2 + 4 * lane + 3] = acc.w;
-        } else {
-          const float inv = 1.f / lsum;
-          float r[4] = {acc.x * inv, acc.y * inv, acc.z * inv, acc.w * inv};
-          if (p.flags & R2K_FLAG_OUTPUT_HADAMARD) {
-#pragma unroll
-            for (int e = 0; e < 4; ++e)  // round through the element type first, as the reference does
-              r[e] = BF16 ? __bfloat162float(__float2bfloat16_rn(r[e])) : __half2float(__float2half_rn(r[e]));
-            float a = r[0] + r[1], bq = r[0] - r[1], c = r[2] + r[3], d = r[2] - r[3];
-            r[0] = a + c; r[1] = bq + d; r[2] = a - c; r[3] = bq - d;
-#pragma unroll
-            for (int sft = 1; sft < 32; sft <<= 1) {
-#pragma unroll
-              for (int e = 0; e < 4; ++e) {
-                const float o2 = __shfl_xor_sync(0xffffffffu, r[e], sft);
-                r[e] = (lane & sft) ? (o2 - r[e]) : (r[e] + o2);
-              }
-            }
-#pragma unroll
-            for (int e = 0; e < 4; ++e) r[e] *= 0.08838834764831845f;
-          }
-          if (p.flags & R2K_FLAG_OUT_F32) {
-            *reinterpret_cast<float4*>(reinterpret_cast<float*>(p.out) + orow * kD + 4 * lane) = make_float4(r[0], r[1], r[2], r[3]);
-          } else {
-            uint2 pk;
-            if (BF16) { pk.x = pack_bf16x2(r[0], r[1]); pk.y = pack_bf16x2(r[2], r[3]); }
-            else { pk.x = pack_f16x2(r[0], r[1]); pk.y = pack_f16x2(r[2], r[3]); }
-            *reinterpret_cast<uint2*>(reinterpret_cast<uint16_t*>(p.out) + orow * kD + 4 * lane) = pk;
-          }
-        }
+        named_bar_sync(1, kConsumers);
+        last = flags[1] != 0;
+        if (last) merge_rows(p.group_partials + (size_t)bh * p.groups_cap * kSlotFloats, ngroups, hh, sub, mx, lsum, acc);
       }
+    }
+    if (last) {
+      // ---- last arriver of (b, h): epilogue and fused append ----
+      write_output<BF16>(p, (size_t)b * p.g.num_q_heads + h * p.gqa + hh, hh < p.gqa, sub, mx, lsum, acc);
       if (has_append && warp == 0) {  // ring row rlen0 of head h
         const size_t src = ((size_t)b * p.g.num_kv_heads + h) * 256 + 8 * lane;
         const size_t dst = ((size_t)h * p.g.recent_capacity + rlen0) * 256 + 8 * lane;
@@ -704,7 +845,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const __gr
       }
       named_bar_sync(1, kConsumers);
       if (threadIdx.x == 0) {
-        p.bh_counter[bh] = 0;
         __threadfence();
         const int done = atomicAdd(&p.req_counter[b], 1);
         if (done == p.g.num_kv_heads - 1) {  // every head of request b is merged: nobody reads recent_len[b] any more

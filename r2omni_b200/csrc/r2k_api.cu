@@ -74,16 +74,32 @@ int derive(const R2KGeom* g, DecodeParams* p) {
   p->units = p->nF + p->n4 + p->n2 + p->nR;
   if (p->units == 0) return R2K_ERR_EMPTY;
   const int g2 = kD / g->v2_group;
-  p->cF = (int64_t)kTF * (64 + 256 + 384 / g->k_block);
-  p->c4 = (int64_t)kTQ * (64 + 68 + 384 / g->k_block);
-  p->c2 = (int64_t)kTQ * (64 + 32 + 3 * g2 + 384 / g->k_block);
-  p->cR = (int64_t)kTR * 512;
-  p->c_bh = p->nF * p->cF + p->n4 * p->c4 + p->n2 * p->c2 + p->nR * p->cR;
-  p->c_total = p->c_bh * p->bh_total;
+  // Tile costs balance the CTAs' work.  The kernel is instruction-bound rather than byte-bound, so the weights
+  // are measured per-tile times (ns of one CTA slot on B200, pure-pool caches), scaled down until a whole
+  // (request, kv head) fits in 22 bits: the kernel's partition arithmetic is 32-bit.
+  (void)g2;
+  const double ns[4] = {1800.0, 2730.0, 2980.0, 900.0};
+  const int64_t cnt[4] = {p->nF, p->n4, p->n2, p->nR};
+  double scale = 100.0;
+  uint32_t w[4];
+  for (;;) {
+    int64_t sum = 0;
+    for (int k = 0; k < 4; ++k) {
+      const double v = ns[k] / scale;
+      w[k] = v < 1.0 ? 1u : (uint32_t)(v + 0.5);
+      sum += cnt[k] * (int64_t)w[k];
+    }
+    if (sum < (1 << 22)) { p->c_bh = (uint32_t)sum; break; }
+    if (w[0] == 1 && w[1] == 1 && w[2] == 1 && w[3] == 1) return R2K_ERR_GEOMETRY;  // > 4M tiles per head
+    scale *= 2.0;
+  }
+  p->cF = w[0]; p->c4 = w[1]; p->c2 = w[2]; p->cR = w[3];
   const int64_t total_units = (int64_t)p->units * p->bh_total;
   const int64_t cap = (int64_t)dev->sms * kCtasPerSm;
   p->grid = (int)(total_units < cap ? total_units : cap);
+  if ((int64_t)p->grid * p->bh_total >= (int64_t)1 << 31) return R2K_ERR_GEOMETRY;
   p->parts_cap = (p->grid + p->bh_total - 1) / p->bh_total + 1;
+  p->groups_cap = (p->parts_cap + 31) / 32;
   p->groups2 = g2;
   p->group2_shift = ilog2(g->v2_group);
   p->kblock_shift = ilog2(g->k_block);
@@ -93,8 +109,12 @@ int derive(const R2KGeom* g, DecodeParams* p) {
 }
 
 size_t counters_bytes(const DecodeParams& p) {
-  const size_t n = (size_t)(p.bh_total + p.g.batch) * sizeof(int);
+  const size_t n = (size_t)(p.bh_total + p.g.batch + p.bh_total * p.groups_cap) * sizeof(int);
   return (n + 255) / 256 * 256;
+}
+size_t workspace_need(const DecodeParams& p) {
+  return kWsHeaderBytes + counters_bytes(p) +
+         (size_t)p.bh_total * (p.parts_cap + p.groups_cap) * kSlotFloats * sizeof(float);
 }
 
 template <bool BF16>
@@ -173,7 +193,7 @@ int r2k_decode_workspace_bytes(const R2KGeom* geom, size_t* bytes) {
   DecodeParams p;
   rc = derive(geom, &p);
   if (rc) return rc;
-  *bytes = kWsHeaderBytes + counters_bytes(p) + (size_t)p.bh_total * p.parts_cap * kSlotFloats * sizeof(float);
+  *bytes = workspace_need(p);
   return R2K_OK;
 }
 
@@ -193,8 +213,7 @@ int r2k_decode(const R2KGeom* geom, const R2KCacheView* view, const void* q, con
   DecodeParams p;
   rc = derive(geom, &p);
   if (rc) return rc;
-  const size_t need = kWsHeaderBytes + counters_bytes(p) + (size_t)p.bh_total * p.parts_cap * kSlotFloats * sizeof(float);
-  if (workspace_bytes < need) return R2K_ERR_WORKSPACE;
+  if (workspace_bytes < workspace_need(p)) return R2K_ERR_WORKSPACE;
   if (!aligned16(workspace) || !aligned16(q) || !aligned16(out)) return R2K_ERR_ALIGNMENT;
   const bool need_k = geom->n_fp + geom->n_i4 + geom->n_i2 > 0;
   if (need_k && (!view->k_packed || !view->k_scale || !view->k_zero)) return R2K_ERR_NULL;
@@ -228,7 +247,9 @@ int r2k_decode(const R2KGeom* geom, const R2KCacheView* view, const void* q, con
   p.err = reinterpret_cast<int*>(ws);
   p.bh_counter = reinterpret_cast<int*>(ws + kWsHeaderBytes);
   p.req_counter = p.bh_counter + p.bh_total;
+  p.group_counter = p.req_counter + p.g.batch;
   p.partials = reinterpret_cast<float*>(ws + kWsHeaderBytes + counters_bytes(p));
+  p.group_partials = p.partials + (size_t)p.bh_total * p.parts_cap * kSlotFloats;
 
   DeviceInfo* dev;
   rc = device_info(&dev);
