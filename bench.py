@@ -252,13 +252,10 @@ def sharded_1m(device, rank, world, steps, warmup, dist_on):
     """Sequence-sharded decode of a 1,048,576-token cache (INT4/INT2 value pages 50/50,
     128-token residual window on the last rank): per-rank un-normalised state, one
     all-gather over NCCL, merge on every rank."""
-    import ctypes as C
-
     import torch.distributed as dist
 
     import r2omni_b200 as R
     from gpu_helpers import make_plan
-    from r2omni_b200 import _lib as L
 
     total = 1 << 20
     per = total // world
@@ -279,23 +276,34 @@ def sharded_1m(device, rank, world, steps, warmup, dist_on):
                                      logical_position=total + i, stats=st)
     a = cache.arenas
     my_bytes = algorithmic_bytes(a.n_fp, a.n_i4, a.i2_active, a.recent_len, 1, append=False)
-    state = torch.empty(1, HQ, 130, device=device, dtype=torch.float32)
-    gathered = torch.empty(world, 1, HQ, 130, device=device, dtype=torch.float32)
-    out = torch.empty(1, HQ, D, device=device, dtype=torch.bfloat16)
-    stream = torch.cuda.current_stream(device)
+    sharded = R.SequenceShardedExecutor(ex) if world > 1 else None
 
     def one_step():
         if world == 1:
             ex(q)
-            return
-        ex.decode_state(q, out=state)
-        dist.all_gather_into_tensor(gathered, state)
-        L.check(L.lib().r2k_merge_states(C.c_void_p(gathered.data_ptr()), world, C.c_int64(HQ * 130), HQ, L.DTYPE_BF16,
-                                         C.c_void_p(out.data_ptr()), C.c_uint32(0), C.c_void_p(stream.cuda_stream)))
+        else:
+            sharded(q)
 
     for _ in range(max(warmup, 3)):
         one_step()
-    ms, _ = time_region(device, lambda: [one_step() for _ in range(steps)], dist_on)
+    # eight steps per CUDA graph (the all-gather is captured too); eager launches if capture is refused
+    torch.cuda.synchronize(device)
+    graph, per_replay = None, 8
+    try:
+        graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(graph):
+            for _ in range(per_replay):
+                one_step()
+        graph.replay()
+        torch.cuda.synchronize(device)
+    except Exception:
+        graph = None
+        torch.cuda.synchronize(device)
+    if graph is not None:
+        steps = max(per_replay, steps // per_replay * per_replay)
+        ms, _ = time_region(device, lambda: [graph.replay() for _ in range(steps // per_replay)], dist_on)
+    else:
+        ms, _ = time_region(device, lambda: [one_step() for _ in range(steps)], dist_on)
     bytes_all = torch.tensor([float(my_bytes)], device=device, dtype=torch.float64)
     if dist_on:
         dist.all_reduce(bytes_all)
@@ -303,7 +311,7 @@ def sharded_1m(device, rank, world, steps, warmup, dist_on):
     return {"workload": "sharded_1m_b1", "tokens": total, "n_gpus": world, "us_per_step": round(us, 2),
             "gbps": round(float(bytes_all.item()) / (us * 1e-6) / 1e9, 1), "steps": steps,
             "collective": "none" if world == 1 else "nccl all_gather of [Hq,130] fp32 per rank",
-            "launches_per_step": 1 if world == 1 else 2}
+            "launches_per_step": 1 if world == 1 else 2, "cuda_graph": graph is not None}
 
 
 def cpu_baseline_sample(tokens, seconds=12.0):

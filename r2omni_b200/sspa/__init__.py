@@ -13,6 +13,7 @@ from .cache import (
     precision_cache_storage_breakdown,
 )
 from .dynamic import DynamicCacheStats, append_generated_token, flush_recent
+from .sharded import SequenceShardedExecutor, shard_token_range
 from .executor import (
     SplitKExecutor,
     SplitKWorkspace,
@@ -32,5 +33,5 @@ __all__ = [
     "DynamicCacheStats", "append_generated_token", "flush_recent",
     "SplitKExecutor", "SplitKWorkspace", "allocate_splitk_workspace", "allocated_workspace_bytes",
     "append_recent_fp", "append_recent_fp_triton", "prepare_splitk_executor", "required_splitk_blocks",
-    "stack_homogeneous_splitk_executors",
+    "stack_homogeneous_splitk_executors", "SequenceShardedExecutor", "shard_token_range",
 ]

@@ -196,13 +196,17 @@ class SplitKExecutor:
             self.arenas.recent_len += 1
         return out
 
-    def decode_state(self, query: torch.Tensor, out: torch.Tensor | None = None) -> torch.Tensor:
+    def decode_state(self, query: torch.Tensor, out: torch.Tensor | None = None, append=None) -> torch.Tensor:
         """Un-normalised (max, sum-exp, weighted V) per query head, float32
-        [B,Hq,130] in natural-log units: the per-shard half of a sequence-sharded decode."""
+        [B,Hq,130] in natural-log units: the per-shard half of a sequence-sharded decode.
+        A shard without any token yields (-inf, 0, 0)."""
         query = self._check_query(query)
+        ap = self._make_append(append, query)
         if out is None:
             out = torch.empty((self.arenas.batch, self.num_query_heads, 130), device=query.device, dtype=torch.float32)
-        self._launch(query, None, out.data_ptr(), L.FLAG_OUT_STATE)
+        self._launch(query, ap, out.data_ptr(), L.FLAG_OUT_STATE)
+        if append is not None and self.batched:
+            self.arenas.recent_len += 1
         return out
 
     def device_status(self) -> int:
