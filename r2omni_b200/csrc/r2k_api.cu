@@ -97,6 +97,8 @@ int derive(const R2KGeom* g, DecodeParams* p) {
   const int64_t total_units = (int64_t)p->units * p->bh_total;
   const int64_t cap = (int64_t)dev->sms * kCtasPerSm;
   p->grid = (int)(total_units < cap ? total_units : cap);
+  // a whole number of CTAs per (request, kv head) when there is room: no CTA pays the partial/merge protocol twice
+  if (p->grid >= 2 * p->bh_total) p->grid = p->grid / p->bh_total * p->bh_total;
   if ((int64_t)p->grid * p->bh_total >= (int64_t)1 << 31) return R2K_ERR_GEOMETRY;
   p->parts_cap = (p->grid + p->bh_total - 1) / p->bh_total + 1;
   p->groups_cap = (p->parts_cap + 31) / 32;
