@@ -147,6 +147,31 @@ int r2k_decode_workspace_init(void* workspace, size_t bytes, void* stream);
 int r2k_decode(const R2KGeom* geom, const R2KCacheView* view, const void* q, const R2KAppend* append,
                void* workspace, size_t workspace_bytes, void* out, uint32_t flags, void* stream);
 
+/*
+ * r2k_decode for callers that are not allowed to allocate device memory: it takes no workspace.
+ * (No counterpart in the reference, which allocates its split-K scratch with torch.)
+ *
+ * Meant for code that runs where cudaMalloc is off limits -- a plugin handed only its input and
+ * output buffers by a host runtime that owns every allocation and forbids others, or a latency
+ * path that must never touch the allocator (cudaMalloc may synchronise the whole device).
+ * The split-K scratch (arrival counters and partial (max, sum-exp, out) slots) lives in a
+ * file-scope `static __device__` array of R2K_STATIC_WORKSPACE_BYTES inside the library, so every GPU
+ * that loads the library holds that much memory until the process exits.
+ *
+ *  - A geometry whose scratch need (r2k_decode_workspace_bytes) exceeds R2K_STATIC_WORKSPACE_BYTES is
+ *    rejected with R2K_ERR_WORKSPACE; nothing is launched.
+ *  - The first call on each device resolves the array's device address (cudaGetSymbolAddress, with
+ *    that device current) and clears its counters; make that first call outside any stream capture.
+ *  - Every call on a device shares the one array, which keeps the previous call's contents.  The
+ *    kernel re-zeroes the counters it used, so back-to-back calls on ONE stream are fine; calls that
+ *    may overlap on the GPU (different streams, or graphs replayed concurrently) race on it and must
+ *    be serialised by the caller, or use r2k_decode with separate workspaces.
+ *  - Inputs, outputs, flags and results are exactly those of r2k_decode.
+ */
+#define R2K_STATIC_WORKSPACE_BYTES (4u << 20)
+int r2k_decode_static(const R2KGeom* geom, const R2KCacheView* view, const void* q, const R2KAppend* append,
+                      void* out, uint32_t flags, void* stream);
+
 /* Copies the device-side status word of the last decodes that used `workspace`
  * into *status (R2K_OK or R2K_ERR_DEVICE_TIMEOUT).  Synchronises `stream`.     */
 int r2k_decode_device_status(void* workspace, int32_t* status, void* stream);

@@ -2,6 +2,7 @@
 // No torch types, no allocation, no synchronisation (except r2k_decode_device_status).
 #include <atomic>
 #include <cstring>
+#include <mutex>
 
 #include "decode_kernel.cuh"
 #include "pack_kernels.cuh"
@@ -271,6 +272,43 @@ int r2k_decode(const R2KGeom* geom, const R2KCacheView* view, const void* q, con
     decode_kernel<false><<<p.grid, kThreads, kSmemBytes, st>>>(p);
   ++g_launches;
   return cudaGetLastError() == cudaSuccess ? R2K_OK : R2K_ERR_CUDA;
+}
+
+}  // extern "C"
+
+// Scratch of r2k_decode_static.  In host code this name is only a handle: the device address comes from
+// cudaGetSymbolAddress, per device (device code may name the array directly).
+static __device__ __align__(256) unsigned char g_static_workspace[R2K_STATIC_WORKSPACE_BYTES];
+
+namespace {
+std::mutex g_static_mutex;
+void* g_static_ptr[64] = {};
+}  // namespace
+
+extern "C" {
+
+int r2k_decode_static(const R2KGeom* geom, const R2KCacheView* view, const void* q, const R2KAppend* append, void* out,
+                      uint32_t flags, void* stream) {
+  size_t need = 0;
+  int rc = r2k_decode_workspace_bytes(geom, &need);
+  if (rc) return rc;
+  if (need > (size_t)R2K_STATIC_WORKSPACE_BYTES) return R2K_ERR_WORKSPACE;
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return R2K_ERR_CUDA;
+  void* ptr = nullptr;
+  {
+    std::lock_guard<std::mutex> lock(g_static_mutex);
+    if (g_static_ptr[dev] == nullptr) {
+      // first call on this device (which is current): resolve the device address of the array and clear the
+      // header and counters at its head; partial slots need no clearing (written before they are read)
+      void* p = nullptr;
+      if (cudaGetSymbolAddress(&p, g_static_workspace) != cudaSuccess || p == nullptr) return R2K_ERR_CUDA;
+      if (cudaMemsetAsync(p, 0, 1u << 16, reinterpret_cast<cudaStream_t>(stream)) != cudaSuccess) return R2K_ERR_CUDA;
+      g_static_ptr[dev] = p;
+    }
+    ptr = g_static_ptr[dev];
+  }
+  return r2k_decode(geom, view, q, append, ptr, (size_t)R2K_STATIC_WORKSPACE_BYTES, out, flags, stream);
 }
 
 int r2k_decode_device_status(void* workspace, int32_t* status, void* stream) {
