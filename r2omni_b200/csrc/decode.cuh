@@ -8,18 +8,18 @@
 namespace r2k {
 
 constexpr int kD = 128;                     // head_dim
-constexpr int kNW = 4;                      // consumer warps per CTA
+constexpr int kNW = 8;                      // consumer warps per CTA
 constexpr int kThreads = (kNW + 1) * 32;    // plus one producer warp
 constexpr int kConsumers = kNW * 32;
 constexpr int kTQ = kNW * 32;               // tokens per tile: INT4-/INT2-value pools (one key block per warp)
 constexpr int kTF = kNW * 16;               // tokens per tile: bf16-value pool
 constexpr int kTR = 32;                     // tokens per tile: residual window (two warps)
 constexpr int kStages = 3;
-constexpr int kCtasPerSm = 2;
+constexpr int kCtasPerSm = 1;
 
 // shared-memory stage: [value region | key payload | key scales | key zeros]
 constexpr int kOffV = 0;
-constexpr int kVBytes = 16384;
+constexpr int kVBytes = kTF * 256;
 constexpr int kOffK = kOffV + kVBytes;
 constexpr int kOffKS = kOffK + kTQ * 64;
 constexpr int kOffKZ = kOffKS + (kTQ / 32) * 256;

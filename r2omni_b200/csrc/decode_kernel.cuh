@@ -218,10 +218,11 @@ __device__ __forceinline__ void mask_scores(float (&s)[4], int row_a, int lo, in
 }
 
 // O^T += V^T P^T for one 16-token tile of INT4 values (codes as subnormals, scale folded into P).
+template <bool PARTIAL>
 __device__ __forceinline__ void pv_int4(WarpState& st, const uint8_t* vrows, const float* vscale, float (&p)[4],
-                                        int g, int t, int pg, int row0, int lo, int hi, bool partial) {
+                                        int g, int t, int pg, int row0, int lo, int hi) {
   float sa = vscale[pg], sb = vscale[pg + 8];
-  if (partial) {
+  if (PARTIAL) {
     if (row0 + pg < lo || row0 + pg >= hi) sa = 0.f;
     if (row0 + pg + 8 < lo || row0 + pg + 8 >= hi) sb = 0.f;
   }
@@ -265,9 +266,9 @@ __device__ __forceinline__ void dequant_crumbs(uint32_t x, const uint32_t (&zm)[
 }
 
 // O^T += V^T P^T for one 16-token tile of INT2 values, dequantised in registers.
+template <bool PARTIAL>
 __device__ __forceinline__ void pv_int2(WarpState& st, const uint8_t* vrows, const uint8_t* vscale, const uint8_t* vzero,
-                                        const DecodeParams& p, float (&pr)[4], int g, int t, int row0, int lo, int hi,
-                                        bool partial) {
+                                        const DecodeParams& p, float (&pr)[4], int g, int t, int row0, int lo, int hi) {
   const uint32_t b0 = movmatrix_trans(pack_f16x2(pr[0], pr[1])), b1 = movmatrix_trans(pack_f16x2(pr[2], pr[3]));
   const int t0 = 2 * t + (t & 1), t1 = 2 * t + 1 - (t & 1);
   const int tok[4] = {t0, t1, t0 + 8, t1 + 8};
@@ -278,7 +279,7 @@ __device__ __forceinline__ void pv_int2(WarpState& st, const uint8_t* vrows, con
     w[i] = *reinterpret_cast<const uint32_t*>(vrows + tok[i] * 32 + 4 * g);
     sc[i] = *reinterpret_cast<const uint16_t*>(vscale + (tok[i] * p.groups2 + grp) * 2);
     zp[i] = vzero[tok[i] * p.groups2 + grp];
-    if (partial && (row0 + tok[i] < lo || row0 + tok[i] >= hi)) { sc[i] = 0u; zp[i] = 0u; }
+    if (PARTIAL && (row0 + tok[i] < lo || row0 + tok[i] >= hi)) { sc[i] = 0u; zp[i] = 0u; }
   }
   uint32_t va[16], vb[16];
 #pragma unroll
@@ -361,6 +362,33 @@ __device__ __forceinline__ void qk_fp(const uint8_t* krows, const uint16_t* qrow
   }
 #pragma unroll
   for (int c = 0; c < 4; ++c) s[c] = acc[c] * scale;
+}
+
+// One warp's 32-token key block of an INT4-/INT2-value tile: scores, softmax update, value accumulation.
+template <bool PARTIAL, bool BF16>
+__device__ __forceinline__ void consume_packed(WarpState& st, const DecodeParams& p, const uint8_t* sb, int pool, int r0,
+                                               int blk, int lo, int hi, const uint32_t (&qh)[16], int g, int t, int pg) {
+  float s[2][4];
+  qk_int4<2>(sb + kOffK + r0 * 64, sb + kOffKS + blk * 256, sb + kOffKZ + blk * 128, qh, t, pg, p.qscale, s);
+  if (PARTIAL) { mask_scores(s[0], pg, lo, hi); mask_scores(s[1], 16 + pg, lo, hi); }
+  softmax_update<2>(st, s);
+  if (pool == 1) {
+    set_units(st, 1);
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+      pv_int4<PARTIAL>(st, sb + kOffV + (r0 + 16 * j) * 64, reinterpret_cast<const float*>(sb + kOffV + kOffI4Scale) + r0 + 16 * j,
+                       s[j], g, t, pg, 16 * j, lo, hi);
+  } else if (pool == 2) {
+    set_units(st, 0);
+#pragma unroll
+    for (int j = 0; j < 2; ++j)
+      pv_int2<PARTIAL>(st, sb + kOffV + (r0 + 16 * j) * 32, sb + kOffV + kOffI2Scale + (r0 + 16 * j) * p.groups2 * 2,
+                       sb + kOffV + kOffI2Zero + (r0 + 16 * j) * p.groups2, p, s[j], g, t, 16 * j, lo, hi);
+  } else {
+    set_units(st, 0);
+#pragma unroll
+    for (int j = 0; j < 2; ++j) pv_fp<BF16>(st, sb + kOffV + (r0 + 16 * j) * 256, s[j], g, t);
+  }
 }
 
 // ---------------------------------------------------------------------------
@@ -497,11 +525,7 @@ __device__ __forceinline__ void produce_full_tile(const DecodeParams& p, const T
 // Loads are issued eight rows at a time so that their latencies overlap.
 __device__ __forceinline__ void merge_rows(const float* base, int count, int hh, int sub, float& mx, float& lsum,
                                            float (&acc)[8]) {
-  float m = -INFINITY;
-  for (int q = sub; q < count; q += 16) m = fmaxf(m, __ldcg(base + (size_t)q * kSlotFloats + hh * kRowFloats));
-#pragma unroll
-  for (int d = 1; d < 16; d <<= 1) m = fmaxf(m, __shfl_xor_sync(0xffffffffu, m, d));
-  mx = m;
+  mx = -INFINITY;
   lsum = 0.f;
 #pragma unroll
   for (int e = 0; e < 8; ++e) acc[e] = 0.f;
@@ -515,6 +539,16 @@ __device__ __forceinline__ void merge_rows(const float* base, int count, int hh,
       ml[k] = __ldcg(reinterpret_cast<const float2*>(row));
       va[k] = __ldcg(reinterpret_cast<const float4*>(row + 4 + 8 * sub));
       vb[k] = __ldcg(reinterpret_cast<const float4*>(row + 8 + 8 * sub));
+    }
+    float bm = mx;   // running reference point: rescale what is already accumulated when a batch raises it
+#pragma unroll
+    for (int k = 0; k < 8; ++k) bm = fmaxf(bm, (q0 + k < count) ? ml[k].x : -INFINITY);
+    if (bm > mx) {
+      const float f = mx == -INFINITY ? 0.f : ex2_approx(mx - bm);
+      lsum *= f;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) acc[e] *= f;
+      mx = bm;
     }
 #pragma unroll
     for (int k = 0; k < 8; ++k) {
@@ -621,12 +655,16 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const __gr
       const int b = bh / p.g.num_kv_heads, h = bh - b * p.g.num_kv_heads;
       int u0, u1;
       unit_range(p, c0, c1, bh, u0, u1);
-      const int rlen = *reinterpret_cast<const int*>((const uint8_t*)p.v.recent_len + (size_t)b * p.v.recent_len_bstride) +
-                       (has_append ? 1 : 0);
+      int rlen = -1;   // read only when a residual-window tile comes up: keeps the load off the path to the first copy
       const TileSources src = tile_sources(p, b, h);
       for (int u = u0; u < u1; ++u) {
         const Tile tl = tile_of(p, u);
-        if (tl.pool == 3 && tl.win >= rlen) continue;
+        if (tl.pool == 3) {
+          if (rlen < 0)
+            rlen = *reinterpret_cast<const int*>((const uint8_t*)p.v.recent_len + (size_t)b * p.v.recent_len_bstride) +
+                   (has_append ? 1 : 0);
+          if (tl.win >= rlen) continue;
+        }
         if (!mbar_wait(&empty_bar[stage], phase ^ 1u)) {
           if (lane == 0) atomicExch(p.err, R2K_ERR_DEVICE_TIMEOUT);
           alive = false;
@@ -683,46 +721,18 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const __gr
       }
       if (alive) {
         uint8_t* sb = stages + stage * kStageBytes;
-        if (tl.pool == 1 || tl.pool == 2) {
-          const int r0 = 32 * warp;  // this warp's key block inside the window
-          const int lo = max(tl.lo - r0, 0), hi = min(tl.hi - r0, 32);
-          if (hi > lo) {
-            const bool partial = (lo > 0) | (hi < 32);
-            const int blk = ((tl.win + r0) >> p.kblock_shift) - (tl.win >> p.kblock_shift);
-            float s[2][4];
-            qk_int4<2>(sb + kOffK + r0 * 64, sb + kOffKS + blk * 256, sb + kOffKZ + blk * 128, qh, t, pg, p.qscale, s);
-            if (partial) { mask_scores(s[0], pg, lo, hi); mask_scores(s[1], 16 + pg, lo, hi); }
-            softmax_update<2>(st, s);
-            if (tl.pool == 1) {
-              set_units(st, 1);
-#pragma unroll
-              for (int j = 0; j < 2; ++j)
-                pv_int4(st, sb + kOffV + (r0 + 16 * j) * 64, reinterpret_cast<const float*>(sb + kOffV + kOffI4Scale) + r0 + 16 * j,
-                        s[j], g, t, pg, 16 * j, lo, hi, partial);
-            } else {
-              set_units(st, 0);
-#pragma unroll
-              for (int j = 0; j < 2; ++j)
-                pv_int2(st, sb + kOffV + (r0 + 16 * j) * 32, sb + kOffV + kOffI2Scale + (r0 + 16 * j) * p.groups2 * 2,
-                        sb + kOffV + kOffI2Zero + (r0 + 16 * j) * p.groups2, p, s[j], g, t, 16 * j, lo, hi, partial);
-            }
-          }
-        } else if (tl.pool == 0) {
-          // 64-token tile = two key blocks: warps {0,1} take even tiles, {2,3} odd ones, 32 tokens per warp,
-          // so the per-block work (Q' and zero-point chain) is paid once per 32 tokens here as well
-          if (((u ^ (warp >> 1)) & 1) == 0) {
-            const int r0 = 32 * (warp & 1);
+        if (tl.pool < 3) {
+          // INT4-/INT2-value tiles: 128 tokens, one key block per warp.  bf16-value tiles: 64 tokens = two key
+          // blocks; the lower half of the warps takes even tiles and the upper half odd ones, so every warp still works on 32 tokens at a
+          // time and pays the per-block work (Q' and the zero-point chain) once per 32 tokens.
+          constexpr int kHalf = kNW / 2;
+          const bool mine = tl.pool != 0 || ((u & 1) == (warp >= kHalf ? 1 : 0));
+          if (mine) {
+            const int r0 = tl.pool != 0 ? 32 * warp : 32 * (warp % kHalf);
             const int lo = max(tl.lo - r0, 0), hi = min(tl.hi - r0, 32);
-            if (hi > lo) {
-              const int blk = ((tl.win + r0) >> p.kblock_shift) - (tl.win >> p.kblock_shift);
-              float s[2][4];
-              qk_int4<2>(sb + kOffK + r0 * 64, sb + kOffKS + blk * 256, sb + kOffKZ + blk * 128, qh, t, pg, p.qscale, s);
-              if ((lo > 0) | (hi < 32)) { mask_scores(s[0], pg, lo, hi); mask_scores(s[1], 16 + pg, lo, hi); }
-              softmax_update<2>(st, s);
-              set_units(st, 0);
-#pragma unroll
-              for (int j = 0; j < 2; ++j) pv_fp<BF16>(st, sb + kOffV + (r0 + 16 * j) * 256, s[j], g, t);
-            }
+            const int blk = ((tl.win + r0) >> p.kblock_shift) - (tl.win >> p.kblock_shift);
+            if (lo == 0 && hi == 32) consume_packed<false, BF16>(st, p, sb, tl.pool, r0, blk, lo, hi, qh, g, t, pg);
+            else if (hi > lo) consume_packed<true, BF16>(st, p, sb, tl.pool, r0, blk, lo, hi, qh, g, t, pg);
           }
         } else if (warp < 2) {
           const int r0 = 16 * warp;
@@ -776,7 +786,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const __gr
     const int part0 = first_cta_of(p, bh);
     const int nparts = last_cta_of(p, bh) - part0 + 1;
     float* slot = p.partials + ((size_t)bh * p.parts_cap + (cta - part0)) * kSlotFloats;
-    {
+    const bool worker = threadIdx.x < 128;   // warps 0-3 carry the merge protocol; the others only meet the barriers
+    if (worker) {
       const int hh = threadIdx.x >> 4, sub = threadIdx.x & 15;  // 16 threads per head, 8 dims each
       float mw[kNW], mx = -INFINITY;
 #pragma unroll
@@ -801,7 +812,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const __gr
     // ---- two-level exact merge: groups of 32 partials, then the group results ----
     // Release pattern: the CTA barrier orders every thread's partial stores before thread 0's fence, whose
     // cumulativity publishes them before the ticket; the reader side mirrors it (ticket, fence, barrier).
-    const int hh = threadIdx.x >> 4, sub = threadIdx.x & 15;
+    const int hh = (threadIdx.x >> 4) & 7, sub = threadIdx.x & 15;
     const int part = cta - part0, grp = part >> 5, ngroups = (nparts + 31) >> 5;
     const int gsize = min(32, nparts - 32 * grp);
     float mx, lsum, acc[8];
@@ -816,9 +827,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const __gr
     named_bar_sync(1, kConsumers);
     bool last = flags[0] != 0;
     if (last) {
-      merge_rows(p.partials + ((size_t)bh * p.parts_cap + 32 * grp) * kSlotFloats, gsize, hh, sub, mx, lsum, acc);
+      if (worker) merge_rows(p.partials + ((size_t)bh * p.parts_cap + 32 * grp) * kSlotFloats, gsize, hh, sub, mx, lsum, acc);
       if (ngroups > 1) {
-        store_row(p.group_partials + ((size_t)bh * p.groups_cap + grp) * kSlotFloats, hh, sub, mx, lsum, acc);
+        if (worker) store_row(p.group_partials + ((size_t)bh * p.groups_cap + grp) * kSlotFloats, hh, sub, mx, lsum, acc);
         named_bar_sync(1, kConsumers);
         if (threadIdx.x == 0) {
           __threadfence();
@@ -829,12 +840,12 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const __gr
         }
         named_bar_sync(1, kConsumers);
         last = flags[1] != 0;
-        if (last) merge_rows(p.group_partials + (size_t)bh * p.groups_cap * kSlotFloats, ngroups, hh, sub, mx, lsum, acc);
+        if (last && worker) merge_rows(p.group_partials + (size_t)bh * p.groups_cap * kSlotFloats, ngroups, hh, sub, mx, lsum, acc);
       }
     }
     if (last) {
       // ---- last arriver of (b, h): epilogue and fused append ----
-      write_output<BF16>(p, (size_t)b * p.g.num_q_heads + h * p.gqa + hh, hh < p.gqa, sub, mx, lsum, acc);
+      if (worker) write_output<BF16>(p, (size_t)b * p.g.num_q_heads + h * p.gqa + hh, hh < p.gqa, sub, mx, lsum, acc);
       if (has_append && warp == 0) {  // ring row rlen0 of head h
         const size_t src = ((size_t)b * p.g.num_kv_heads + h) * 256 + 8 * lane;
         const size_t dst = ((size_t)h * p.g.recent_capacity + rlen0) * 256 + 8 * lane;
