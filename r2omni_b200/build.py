@@ -11,7 +11,7 @@ ROOT = os.path.dirname(PKG)
 CSRC = os.path.join(PKG, "csrc")
 LIB = os.path.join(PKG, "lib", "libr2k_b200.so")
 SOURCES = ("r2k_api.cu",)
-HEADERS = ("decode.cuh", "decode_kernel.cuh", "device_utils.cuh", "pack_kernels.cuh")
+HEADERS = ("decode.cuh", "decode_consumer.cuh", "decode_kernel.cuh", "device_utils.cuh", "pack_kernels.cuh")
 
 
 def _stale() -> bool:

@@ -25,6 +25,7 @@ constexpr int kOffKS = kOffK + kTQ * 64;
 constexpr int kOffKZ = kOffKS + (kTQ / 32) * 256;
 constexpr int kStageBytes = kOffKZ + (kTQ / 32) * 128;
 static_assert(kStageBytes % 128 == 0, "stage must stay 128-byte aligned");
+static_assert(kTF % 128 == 0 && kTQ % 128 == 0, "tile windows must start on multiples of the largest key block");
 // value region, per pool
 constexpr int kOffI4Scale = kTQ * 64;            // f32 per token after the nibble rows
 constexpr int kOffI2Scale = kTQ * 32;            // f16 x groups per token after the crumb rows

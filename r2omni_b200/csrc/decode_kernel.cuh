@@ -29,19 +29,12 @@
 #pragma once
 
 #include "decode.cuh"
+#include "decode_consumer.cuh"
 #include "device_utils.cuh"
 
 namespace r2k {
 
 namespace {
-
-constexpr float kLn2 = 0.69314718055994531f;
-constexpr float k2p24 = 16777216.0f;
-constexpr float k2p20 = 1048576.0f;
-constexpr float k2m24 = 1.0f / 16777216.0f;
-constexpr float k2m20 = 1.0f / 1048576.0f;
-constexpr uint32_t kMaskLo = 0x000F000Fu;  // nibble 0 of each half-word -> code * 2^-24 as fp16
-constexpr uint32_t kMaskHi = 0x00F000F0u;  // nibble 1 of each half-word -> code * 2^-20 as fp16
 
 struct Tile {
   int pool;   // 0 bf16-V, 1 INT4-V, 2 INT2-V, 3 residual
@@ -80,317 +73,6 @@ __device__ __forceinline__ float elem_to_float(uint16_t raw) {
   return __half2float(__ushort_as_half(raw));
 }
 
-// Row permutation inside a 16-token MMA tile: MMA row/k-slot r reads token
-// pi(r).  It keeps a thread's two key rows in one 128-byte line and makes the
-// four tokens of one value load alternate 64-byte halves (2-way instead of
-// 4-way shared-memory conflicts).
-__device__ __forceinline__ int pi_row(int r) {  // r in 0..7
-  return (r & ~1) + ((r & 1) ^ ((r >> 1) & 1));
-}
-
-struct WarpState {
-  float m[2];      // running max (log2 units) of heads 2t, 2t+1
-  float l[2];      // this lane's share of sum-exp
-  float lp[2];     // this lane's share of sum of fp16(p * scale) over INT4-value tokens (for the -8 code offset)
-  float o[8][4];   // O^T fragments: block j <-> dims 16g+2j (c0,c1) and 16g+2j+1 (c2,c3); columns = heads 2t,2t+1
-  int units;       // 0: true units; 1: INT4 units (even dims * 2^-24, odd dims * 2^-20)
-};
-
-__device__ __forceinline__ void state_reset(WarpState& s) {
-  s.m[0] = s.m[1] = -INFINITY;
-  s.l[0] = s.l[1] = s.lp[0] = s.lp[1] = 0.f;
-#pragma unroll
-  for (int j = 0; j < 8; ++j) s.o[j][0] = s.o[j][1] = s.o[j][2] = s.o[j][3] = 0.f;
-  s.units = 0;
-}
-
-__device__ __forceinline__ void set_units(WarpState& s, int units) {
-  if (s.units == units) return;
-  const float fe = units ? k2m24 : k2p24, fo = units ? k2m20 : k2p20;  // exact power-of-two rescale
-#pragma unroll
-  for (int j = 0; j < 8; ++j) { s.o[j][0] *= fe; s.o[j][1] *= fe; s.o[j][2] *= fo; s.o[j][3] *= fo; }
-  s.units = units;
-}
-
-// Online-softmax update for NT 16-token tiles of scores (log2 units, already
-// masked with -inf); returns probabilities in place.
-template <int NT>
-__device__ __forceinline__ void softmax_update(WarpState& st, float (&s)[NT][4]) {
-  float mx0 = -INFINITY, mx1 = -INFINITY;
-#pragma unroll
-  for (int j = 0; j < NT; ++j) {
-    mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][2]));
-    mx1 = fmaxf(mx1, fmaxf(s[j][1], s[j][3]));
-  }
-#pragma unroll
-  for (int d = 4; d < 32; d <<= 1) {
-    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, d));
-    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, d));
-  }
-  // Lazy reference point: the running "max" only moves when a score exceeds it by more than 2^8, so
-  // probabilities stay below 256 (exact enough in fp16/fp32) and most blocks skip the rescale.
-  const float n0 = fmaxf(st.m[0], mx0), n1 = fmaxf(st.m[1], mx1);
-  if (__any_sync(0xffffffffu, (mx0 > st.m[0] + 8.f) | (mx1 > st.m[1] + 8.f))) {
-    const float f0 = ex2_approx(st.m[0] - n0), f1 = ex2_approx(st.m[1] - n1);  // m = -inf -> 0
-    st.l[0] *= f0; st.l[1] *= f1; st.lp[0] *= f0; st.lp[1] *= f1;
-#pragma unroll
-    for (int j = 0; j < 8; ++j) { st.o[j][0] *= f0; st.o[j][1] *= f1; st.o[j][2] *= f0; st.o[j][3] *= f1; }
-    st.m[0] = n0; st.m[1] = n1;
-  }
-#pragma unroll
-  for (int j = 0; j < NT; ++j) {
-    s[j][0] = ex2_approx(s[j][0] - st.m[0]);
-    s[j][1] = ex2_approx(s[j][1] - st.m[1]);
-    s[j][2] = ex2_approx(s[j][2] - st.m[0]);
-    s[j][3] = ex2_approx(s[j][3] - st.m[1]);
-    st.l[0] += s[j][0] + s[j][2];
-    st.l[1] += s[j][1] + s[j][3];
-  }
-}
-
-// Scores of NT 16-token tiles against INT4 keys.  krows: shared-memory address
-// of the slice's first key row; ks/kz: the block's scale / zero rows.
-// Q' = q * scale is held as an exact two-term fp16 sum (hi = RN(q*s), lo = fma(q, s, -hi)),
-// so every product the tensor core sees is exact and the fp32 accumulation is the only rounding.
-template <int NT>
-__device__ __forceinline__ void qk_int4(const uint8_t* krows, const uint8_t* ks, const uint8_t* kz,
-                                        const uint32_t (&qh)[16], int t, int pg, float alpha, float (&s)[NT][4]) {
-  uint32_t qp[16], ql[16];  // paired (c0,c4) (c1,c5) (c2,c6) (c3,c7) per 8-channel word
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const uint4 w = *reinterpret_cast<const uint4*>(ks + 64 * t + 16 * i);
-    const uint32_t sp[4] = {__byte_perm(w.x, w.z, 0x5410), __byte_perm(w.x, w.z, 0x7632), __byte_perm(w.y, w.w, 0x5410),
-                            __byte_perm(w.y, w.w, 0x7632)};
-#pragma unroll
-    for (int k = 0; k < 4; ++k) {
-      qp[4 * i + k] = hmul2_u32(qh[4 * i + k], sp[k]);
-      ql[4 * i + k] = hfma2_neg_u32(qh[4 * i + k], sp[k], qp[4 * i + k]);
-    }
-  }
-  // zero-point term sum_c Q'[c] * zero[c], as one more MMA chain whose 16 rows are all the zero row
-  float zc[4];
-  {
-    float zq[4][4];
-    const uint4 za = *reinterpret_cast<const uint4*>(kz + 32 * t);
-    const uint4 zb = *reinterpret_cast<const uint4*>(kz + 32 * t + 16);
-    const uint32_t z[8] = {za.x, za.y, za.z, za.w, zb.x, zb.y, zb.z, zb.w};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const uint32_t x = __byte_perm(z[2 * i], z[2 * i + 1], 0x5410);  // z0 z1 z4 z5
-      const uint32_t y = __byte_perm(z[2 * i], z[2 * i + 1], 0x7632);  // z2 z3 z6 z7
-      const uint32_t r0 = x & 0x00FF00FFu, r1 = __byte_perm(x, 0u, 0x4341);
-      const uint32_t r2 = y & 0x00FF00FFu, r3 = __byte_perm(y, 0u, 0x4341);
-      zq[i][0] = zq[i][1] = zq[i][2] = zq[i][3] = 0.f;   // four independent chains
-      mma_f16(zq[i], r0, r0, r2, r2, qp[4 * i + 0], qp[4 * i + 2]);
-      mma_f16(zq[i], r1, r1, r3, r3, qp[4 * i + 1], qp[4 * i + 3]);
-      mma_f16(zq[i], r0, r0, r2, r2, ql[4 * i + 0], ql[4 * i + 2]);
-      mma_f16(zq[i], r1, r1, r3, r3, ql[4 * i + 1], ql[4 * i + 3]);
-    }
-#pragma unroll
-    for (int c = 0; c < 4; ++c) zc[c] = (zq[0][c] + zq[1][c]) + (zq[2][c] + zq[3][c]);
-  }
-  const float f24 = k2p24 * alpha, f20 = k2p20 * alpha;
-#pragma unroll
-  for (int j = 0; j < NT; ++j) {
-    const uint8_t* r = krows + (16 * j + pg) * 64 + 16 * t;
-    const uint4 ka = *reinterpret_cast<const uint4*>(r);
-    const uint4 kb = *reinterpret_cast<const uint4*>(r + 8 * 64);
-    const uint32_t wa[4] = {ka.x, ka.y, ka.z, ka.w}, wb[4] = {kb.x, kb.y, kb.z, kb.w};
-    float lo[4] = {-zc[0], -zc[1], -zc[2], -zc[3]}, hi[4] = {0.f, 0.f, 0.f, 0.f};
-#pragma unroll
-    for (int i = 0; i < 4; ++i) {
-      const uint32_t a8 = wa[i] >> 8, b8 = wb[i] >> 8;
-      const uint32_t l0 = wa[i] & kMaskLo, l1 = wb[i] & kMaskLo, l2 = a8 & kMaskLo, l3 = b8 & kMaskLo;
-      const uint32_t h0 = wa[i] & kMaskHi, h1 = wb[i] & kMaskHi, h2 = a8 & kMaskHi, h3 = b8 & kMaskHi;
-      mma_f16(lo, l0, l1, l2, l3, qp[4 * i + 0], qp[4 * i + 2]);
-      mma_f16(hi, h0, h1, h2, h3, qp[4 * i + 1], qp[4 * i + 3]);
-      mma_f16(lo, l0, l1, l2, l3, ql[4 * i + 0], ql[4 * i + 2]);
-      mma_f16(hi, h0, h1, h2, h3, ql[4 * i + 1], ql[4 * i + 3]);
-    }
-#pragma unroll
-    for (int c = 0; c < 4; ++c) s[j][c] = fmaf(lo[c], f24, hi[c] * f20);
-  }
-}
-
-__device__ __forceinline__ void mask_scores(float (&s)[4], int row_a, int lo, int hi) {
-  if (row_a < lo || row_a >= hi) s[0] = s[1] = -INFINITY;
-  if (row_a + 8 < lo || row_a + 8 >= hi) s[2] = s[3] = -INFINITY;
-}
-
-// O^T += V^T P^T for one 16-token tile of INT4 values (codes as subnormals, scale folded into P).
-template <bool PARTIAL>
-__device__ __forceinline__ void pv_int4(WarpState& st, const uint8_t* vrows, const float* vscale, float (&p)[4],
-                                        int g, int t, int pg, int row0, int lo, int hi) {
-  float sa = vscale[pg], sb = vscale[pg + 8];
-  if (PARTIAL) {
-    if (row0 + pg < lo || row0 + pg >= hi) sa = 0.f;
-    if (row0 + pg + 8 < lo || row0 + pg + 8 >= hi) sb = 0.f;
-  }
-  const uint32_t ha = pack_f16x2(p[0] * sa, p[1] * sa), hb = pack_f16x2(p[2] * sb, p[3] * sb);
-  {
-    const float2 fa = __half22float2(*reinterpret_cast<const __half2*>(&ha));
-    const float2 fb = __half22float2(*reinterpret_cast<const __half2*>(&hb));
-    st.lp[0] += fa.x + fb.x;
-    st.lp[1] += fa.y + fb.y;
-  }
-  const uint32_t b0 = movmatrix_trans(ha), b1 = movmatrix_trans(hb);
-  const int t0 = 2 * t + (t & 1), t1 = 2 * t + 1 - (t & 1);
-  const uint8_t* base = vrows + 8 * g;
-  const uint2 w0 = *reinterpret_cast<const uint2*>(base + t0 * 64);
-  const uint2 w1 = *reinterpret_cast<const uint2*>(base + t1 * 64);
-  const uint2 w2 = *reinterpret_cast<const uint2*>(base + (t0 + 8) * 64);
-  const uint2 w3 = *reinterpret_cast<const uint2*>(base + (t1 + 8) * 64);
-#pragma unroll
-  for (int hf = 0; hf < 2; ++hf) {
-    const uint32_t c0 = (hf ? w0.y : w0.x) ^ 0x88888888u, c1 = (hf ? w1.y : w1.x) ^ 0x88888888u;
-    const uint32_t c2 = (hf ? w2.y : w2.x) ^ 0x88888888u, c3 = (hf ? w3.y : w3.x) ^ 0x88888888u;
-    const uint32_t xa = __byte_perm(c0, c1, 0x5410), ya = __byte_perm(c0, c1, 0x7632);
-    const uint32_t xb = __byte_perm(c2, c3, 0x5410), yb = __byte_perm(c2, c3, 0x7632);
-    mma_f16(st.o[4 * hf + 0], xa & kMaskLo, xa & kMaskHi, xb & kMaskLo, xb & kMaskHi, b0, b1);
-    mma_f16(st.o[4 * hf + 1], (xa >> 8) & kMaskLo, (xa >> 8) & kMaskHi, (xb >> 8) & kMaskLo, (xb >> 8) & kMaskHi, b0, b1);
-    mma_f16(st.o[4 * hf + 2], ya & kMaskLo, ya & kMaskHi, yb & kMaskLo, yb & kMaskHi, b0, b1);
-    mma_f16(st.o[4 * hf + 3], (ya >> 8) & kMaskLo, (ya >> 8) & kMaskHi, (yb >> 8) & kMaskLo, (yb >> 8) & kMaskHi, b0, b1);
-  }
-}
-
-// (code - zero) * scale for the eight 2-bit fields of each half-word of x -> eight half2.
-__device__ __forceinline__ void dequant_crumbs(uint32_t x, const uint32_t (&zm)[5], const uint32_t (&sk)[5],
-                                               uint32_t (&v)[8]) {
-#pragma unroll
-  for (int i = 0; i < 5; ++i)
-    v[i] = hmul2_u32(hsub2_u32((x & (0x00030003u << (2 * i))) | 0x64006400u, zm[i]), sk[i]);
-  const uint32_t y = x >> 10;
-#pragma unroll
-  for (int i = 0; i < 3; ++i)
-    v[5 + i] = hmul2_u32(hsub2_u32((y & (0x00030003u << (2 * i))) | 0x64006400u, zm[i]), sk[i]);
-}
-
-// O^T += V^T P^T for one 16-token tile of INT2 values, dequantised in registers.
-template <bool PARTIAL>
-__device__ __forceinline__ void pv_int2(WarpState& st, const uint8_t* vrows, const uint8_t* vscale, const uint8_t* vzero,
-                                        const DecodeParams& p, float (&pr)[4], int g, int t, int row0, int lo, int hi) {
-  const uint32_t b0 = movmatrix_trans(pack_f16x2(pr[0], pr[1])), b1 = movmatrix_trans(pack_f16x2(pr[2], pr[3]));
-  const int t0 = 2 * t + (t & 1), t1 = 2 * t + 1 - (t & 1);
-  const int tok[4] = {t0, t1, t0 + 8, t1 + 8};
-  const int grp = (16 * g) >> p.group2_shift;
-  uint32_t w[4], sc[4], zp[4];
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    w[i] = *reinterpret_cast<const uint32_t*>(vrows + tok[i] * 32 + 4 * g);
-    sc[i] = *reinterpret_cast<const uint16_t*>(vscale + (tok[i] * p.groups2 + grp) * 2);
-    zp[i] = vzero[tok[i] * p.groups2 + grp];
-    if (PARTIAL && (row0 + tok[i] < lo || row0 + tok[i] >= hi)) { sc[i] = 0u; zp[i] = 0u; }
-  }
-  uint32_t va[16], vb[16];
-#pragma unroll
-  for (int pr2 = 0; pr2 < 2; ++pr2) {
-    const uint32_t s2 = sc[2 * pr2] | (sc[2 * pr2 + 1] << 16), z2 = zp[2 * pr2] | (zp[2 * pr2 + 1] << 16);
-    uint32_t zm[5], sk[5];
-    const uint32_t quarter[5] = {0x3C003C00u, 0x34003400u, 0x2C002C00u, 0x24002400u, 0x1C001C00u};  // 4^-i as half2
-#pragma unroll
-    for (int i = 0; i < 5; ++i) { zm[i] = 0x64006400u + (z2 << (2 * i)); sk[i] = i ? hmul2_u32(s2, quarter[i]) : s2; }
-    const uint32_t x = __byte_perm(w[2 * pr2], w[2 * pr2 + 1], 0x5410), y = __byte_perm(w[2 * pr2], w[2 * pr2 + 1], 0x7632);
-    uint32_t lo8[8], hi8[8];
-    dequant_crumbs(x, zm, sk, lo8);
-    dequant_crumbs(y, zm, sk, hi8);
-#pragma unroll
-    for (int i = 0; i < 8; ++i) {
-      if (pr2 == 0) { va[i] = lo8[i]; va[8 + i] = hi8[i]; } else { vb[i] = lo8[i]; vb[8 + i] = hi8[i]; }
-    }
-  }
-#pragma unroll
-  for (int j = 0; j < 8; ++j) mma_f16(st.o[j], va[2 * j], va[2 * j + 1], vb[2 * j], vb[2 * j + 1], b0, b1);
-}
-
-// O^T += V^T P^T for one 16-token tile of 16-bit values (rows of 256 bytes).
-template <bool BF16>
-__device__ __forceinline__ void pv_fp(WarpState& st, const uint8_t* vrows, float (&pr)[4], int g, int t) {
-  uint32_t bh0, bh1, bl0 = 0, bl1 = 0;
-  if (BF16) {  // P = P_hi + P_lo in bf16: two MMAs keep ~16 mantissa bits of P
-    const uint32_t ha = pack_bf16x2(pr[0], pr[1]), hb = pack_bf16x2(pr[2], pr[3]);
-    const uint32_t la = pack_bf16x2(pr[0] - __uint_as_float(ha << 16), pr[1] - __uint_as_float(ha & 0xffff0000u));
-    const uint32_t lb = pack_bf16x2(pr[2] - __uint_as_float(hb << 16), pr[3] - __uint_as_float(hb & 0xffff0000u));
-    bh0 = movmatrix_trans(ha); bh1 = movmatrix_trans(hb);
-    bl0 = movmatrix_trans(la); bl1 = movmatrix_trans(lb);
-  } else {
-    bh0 = movmatrix_trans(pack_f16x2(pr[0], pr[1])); bh1 = movmatrix_trans(pack_f16x2(pr[2], pr[3]));
-  }
-  const int t0 = 2 * t + (t & 1), t1 = 2 * t + 1 - (t & 1);
-  const uint8_t* base = vrows + 32 * g;
-#pragma unroll
-  for (int hf = 0; hf < 2; ++hf) {
-    const uint4 r0 = *reinterpret_cast<const uint4*>(base + t0 * 256 + 16 * hf);
-    const uint4 r1 = *reinterpret_cast<const uint4*>(base + t1 * 256 + 16 * hf);
-    const uint4 r2 = *reinterpret_cast<const uint4*>(base + (t0 + 8) * 256 + 16 * hf);
-    const uint4 r3 = *reinterpret_cast<const uint4*>(base + (t1 + 8) * 256 + 16 * hf);
-    const uint32_t a[4] = {r0.x, r0.y, r0.z, r0.w}, b[4] = {r1.x, r1.y, r1.z, r1.w};
-    const uint32_t c[4] = {r2.x, r2.y, r2.z, r2.w}, d[4] = {r3.x, r3.y, r3.z, r3.w};
-#pragma unroll
-    for (int q = 0; q < 4; ++q) {
-      const uint32_t a0 = __byte_perm(a[q], b[q], 0x5410), a1 = __byte_perm(a[q], b[q], 0x7632);
-      const uint32_t a2 = __byte_perm(c[q], d[q], 0x5410), a3 = __byte_perm(c[q], d[q], 0x7632);
-      if (BF16) {
-        mma_bf16(st.o[4 * hf + q], a0, a1, a2, a3, bh0, bh1);
-        mma_bf16(st.o[4 * hf + q], a0, a1, a2, a3, bl0, bl1);
-      } else {
-        mma_f16(st.o[4 * hf + q], a0, a1, a2, a3, bh0, bh1);
-      }
-    }
-  }
-}
-
-// Scores of one 16-token tile of 16-bit keys (residual window): exact products, fp32 accumulation.
-template <bool BF16>
-__device__ __forceinline__ void qk_fp(const uint8_t* krows, const uint16_t* qrow, int t, int pg, float scale,
-                                      float (&s)[4]) {
-  float acc[4] = {0.f, 0.f, 0.f, 0.f};
-  const uint8_t* ra = krows + pg * 256 + 64 * t;
-  const uint8_t* rb = ra + 8 * 256;
-#pragma unroll
-  for (int i = 0; i < 4; ++i) {
-    const uint4 ka = *reinterpret_cast<const uint4*>(ra + 16 * i);
-    const uint4 kb = *reinterpret_cast<const uint4*>(rb + 16 * i);
-    uint4 qq = make_uint4(0u, 0u, 0u, 0u);
-    if (qrow != nullptr) qq = __ldg(reinterpret_cast<const uint4*>(qrow + 32 * t + 8 * i));
-    if (BF16) {
-      mma_bf16(acc, ka.x, kb.x, ka.y, kb.y, qq.x, qq.y);
-      mma_bf16(acc, ka.z, kb.z, ka.w, kb.w, qq.z, qq.w);
-    } else {
-      mma_f16(acc, ka.x, kb.x, ka.y, kb.y, qq.x, qq.y);
-      mma_f16(acc, ka.z, kb.z, ka.w, kb.w, qq.z, qq.w);
-    }
-  }
-#pragma unroll
-  for (int c = 0; c < 4; ++c) s[c] = acc[c] * scale;
-}
-
-// One warp's 32-token key block of an INT4-/INT2-value tile: scores, softmax update, value accumulation.
-template <bool PARTIAL, bool BF16>
-__device__ __forceinline__ void consume_packed(WarpState& st, const DecodeParams& p, const uint8_t* sb, int pool, int r0,
-                                               int blk, int lo, int hi, const uint32_t (&qh)[16], int g, int t, int pg) {
-  float s[2][4];
-  qk_int4<2>(sb + kOffK + r0 * 64, sb + kOffKS + blk * 256, sb + kOffKZ + blk * 128, qh, t, pg, p.qscale, s);
-  if (PARTIAL) { mask_scores(s[0], pg, lo, hi); mask_scores(s[1], 16 + pg, lo, hi); }
-  softmax_update<2>(st, s);
-  if (pool == 1) {
-    set_units(st, 1);
-#pragma unroll
-    for (int j = 0; j < 2; ++j)
-      pv_int4<PARTIAL>(st, sb + kOffV + (r0 + 16 * j) * 64, reinterpret_cast<const float*>(sb + kOffV + kOffI4Scale) + r0 + 16 * j,
-                       s[j], g, t, pg, 16 * j, lo, hi);
-  } else if (pool == 2) {
-    set_units(st, 0);
-#pragma unroll
-    for (int j = 0; j < 2; ++j)
-      pv_int2<PARTIAL>(st, sb + kOffV + (r0 + 16 * j) * 32, sb + kOffV + kOffI2Scale + (r0 + 16 * j) * p.groups2 * 2,
-                       sb + kOffV + kOffI2Zero + (r0 + 16 * j) * p.groups2, p, s[j], g, t, 16 * j, lo, hi);
-  } else {
-    set_units(st, 0);
-#pragma unroll
-    for (int j = 0; j < 2; ++j) pv_fp<BF16>(st, sb + kOffV + (r0 + 16 * j) * 256, s[j], g, t);
-  }
-}
-
 // ---------------------------------------------------------------------------
 // producer
 // ---------------------------------------------------------------------------
@@ -423,11 +105,12 @@ __device__ __forceinline__ void produce_tile(const DecodeParams& p, const Tile& 
     }
   } else {
     const int len = tl.pool == 0 ? kTF : kTQ;
-    // keys: the whole window (always inside the arena: windows and capacity are multiples of the tile)
+    // keys: the whole window, clipped to the arena (its capacity is a multiple of 128 rows, not of the tile)
+    const int krows = min(len, p.g.k_capacity - tl.win);
     copy_piece(stage + kOffK, v.k_packed + (size_t)b * v.k_packed_bstride + ((size_t)h * p.g.k_capacity + tl.win) * 64,
-               len * 64, bar, lane, tx);
+               krows * 64, bar, lane, tx);
     const int blk0 = tl.win >> p.kblock_shift;
-    const int nblk = max(1, len >> p.kblock_shift);
+    const int nblk = min(max(1, len >> p.kblock_shift), (p.g.k_capacity >> p.kblock_shift) - blk0);
     const size_t meta = (size_t)h * (p.g.k_capacity >> p.kblock_shift) + blk0;
     copy_piece(stage + kOffKS, (const uint8_t*)v.k_scale + (size_t)b * v.k_scale_bstride + meta * 256, nblk * 256, bar, lane, tx);
     copy_piece(stage + kOffKZ, v.k_zero + (size_t)b * v.k_zero_bstride + meta * 128, nblk * 128, bar, lane, tx);
@@ -619,6 +302,80 @@ __device__ __forceinline__ void write_output(const DecodeParams& p, size_t orow,
   }
 }
 
+// One warp's 32-token key block of a tile: scores, softmax update, value accumulation.
+template <int POOL, bool PARTIAL, bool BF16>
+__device__ __forceinline__ void consume_block(WarpState& st, uint32_t sb, const LaneOffsets& o, const uint32_t (&qh)[16],
+                                              float alpha, int t, int pg, int step, int lo, int hi) {
+  float s[2][4];
+  qk_int4(sb, o, qh, alpha, s);
+  if (PARTIAL) { mask_scores(s[0], pg, lo, hi); mask_scores(s[1], 16 + pg, lo, hi); }
+  softmax_update<2>(st, s);
+#pragma unroll
+  for (int j = 0; j < 2; ++j) {
+    if (POOL == 0) pv_fp<BF16>(st, sb, o.va, o.vb, j, s[j]);
+    else if (POOL == 1) pv_int4<PARTIAL>(st, sb, o, j, s[j], pg, lo, hi);
+    else pv_int2<PARTIAL>(st, sb, o, j, s[j], t, step, lo, hi);
+  }
+}
+
+// All tiles [ua, ub) of one value pool for one (request, kv head): the lane offsets are computed once here.
+// INT4-/INT2-value tiles hold kTQ tokens, one key block per warp.  bf16-value tiles hold kTF = kTQ/2 tokens;
+// the lower half of the warps takes even tiles and the upper half odd ones, so every warp still works on 32
+// tokens at a time and pays the per-block work (Q' and the zero-point chain) once per 32 tokens.
+template <int POOL, bool BF16>
+__device__ __forceinline__ void consume_pool(WarpState& st, const DecodeParams& p, int ua, int ub, int first, uint32_t stage0,
+                                             uint64_t* full_bar, uint64_t* empty_bar, int& stage, uint32_t& phase, bool& alive,
+                                             const uint32_t (&qh)[16], int warp, int lane) {
+  if (ua >= ub) return;
+  const int g = lane >> 2, t = lane & 3, pg = pi_row(g);
+  constexpr int kLen = POOL == 0 ? kTF : kTQ;
+  constexpr int kHalf = kNW / 2;
+  const int a0 = POOL == 0 ? p.g.k_off_fp : POOL == 1 ? p.g.k_off_i4 : p.g.k_off_i2;
+  const int a1 = a0 + (POOL == 0 ? p.g.n_fp : POOL == 1 ? p.g.n_i4 : p.g.n_i2);
+  const int w0 = POOL == 0 ? p.wF0 : POOL == 1 ? p.w40 : p.w20;
+  const int slice = 32 * (POOL == 0 ? warp % kHalf : warp);
+  const int t0 = 2 * t + (t & 1), t1 = 2 * t + 1 - (t & 1);
+  const int blk = slice >> p.kblock_shift;   // windows start on multiples of the largest key block
+  LaneOffsets o;
+  o.k = kOffK + (slice + pg) * 64 + 16 * t;
+  o.ks = kOffKS + blk * 256 + 64 * t;
+  o.kz = kOffKZ + blk * 128 + 32 * t;
+  int step = 0;
+  if (POOL == 0) {
+    o.va = kOffV + (slice + t0) * 256 + 32 * g; o.vb = kOffV + (slice + t1) * 256 + 32 * g; o.m0 = o.m1 = 0;
+  } else if (POOL == 1) {
+    o.va = kOffV + (slice + t0) * 64 + 8 * g; o.vb = kOffV + (slice + t1) * 64 + 8 * g;
+    o.m0 = kOffV + kOffI4Scale + (slice + pg) * 4; o.m1 = 0;
+  } else {
+    step = 2 * p.groups2;
+    const int grp = (16 * g) >> p.group2_shift;
+    o.va = kOffV + (slice + t0) * 32 + 4 * g; o.vb = kOffV + (slice + t1) * 32 + 4 * g;
+    o.m0 = kOffV + kOffI2Scale + (slice + t0) * step + 2 * grp;
+    o.m1 = kOffV + kOffI2Zero + (slice + t0) * (step >> 1) + grp;
+  }
+  set_units(st, POOL == 1 ? 1 : 0);
+  const int parity = warp >= kHalf ? 1 : 0;
+  int lo_edge = a0 - (w0 + (ua - first) * kLen) - slice;   // validity window of this warp's slice, slides with the tile
+  int hi_edge = a1 - (w0 + (ua - first) * kLen) - slice;
+  for (int u = ua; u < ub; ++u, lo_edge -= kLen, hi_edge -= kLen) {
+    if (alive && !mbar_wait(&full_bar[stage], phase)) {
+      if (lane == 0) atomicExch(p.err, R2K_ERR_DEVICE_TIMEOUT);
+      alive = false;
+    }
+    if (alive) {
+      if (POOL != 0 || ((u & 1) == parity)) {
+        const uint32_t sb = stage0 + stage * kStageBytes;
+        if (lo_edge <= 0 && hi_edge >= 32) consume_block<POOL, false, BF16>(st, sb, o, qh, p.qscale, t, pg, step, 0, 32);
+        else if (min(hi_edge, 32) > max(lo_edge, 0))
+          consume_block<POOL, true, BF16>(st, sb, o, qh, p.qscale, t, pg, step, max(lo_edge, 0), min(hi_edge, 32));
+      }
+      __syncwarp();
+      if (lane == 0) mbar_arrive(&empty_bar[stage]);
+    }
+    if (++stage == kStages) { stage = 0; phase ^= 1u; }
+  }
+}
+
 // ---------------------------------------------------------------------------
 // kernel
 // ---------------------------------------------------------------------------
@@ -665,7 +422,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const __gr
                    (has_append ? 1 : 0);
           if (tl.win >= rlen) continue;
         }
-        if (!mbar_wait(&empty_bar[stage], phase ^ 1u)) {
+        if (!mbar_wait_relaxed(&empty_bar[stage], phase ^ 1u)) {
           if (lane == 0) atomicExch(p.err, R2K_ERR_DEVICE_TIMEOUT);
           alive = false;
           break;
@@ -712,47 +469,43 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const __gr
       for (int k = 0; k < 4; ++k) qh[4 * i + k] = pack_f16x2(f[k], f[k + 4]);
     }
 
-    for (int u = u0; u < u1; ++u) {
-      const Tile tl = tile_of(p, u);
-      if (tl.pool == 3 && tl.win >= rlen) continue;
+    const uint32_t stage0 = smem_u32(stages);
+    consume_pool<0, BF16>(st, p, max(u0, 0), min(u1, p.nF), 0, stage0, full_bar, empty_bar, stage, phase, alive, qh, warp, lane);
+    consume_pool<1, BF16>(st, p, max(u0, p.nF), min(u1, p.nF + p.n4), p.nF, stage0, full_bar, empty_bar, stage, phase, alive,
+                          qh, warp, lane);
+    consume_pool<2, BF16>(st, p, max(u0, p.nF + p.n4), min(u1, p.nF + p.n4 + p.n2), p.nF + p.n4, stage0, full_bar, empty_bar,
+                          stage, phase, alive, qh, warp, lane);
+    // residual window: 32-token tiles, 16 tokens for each of warps 0 and 1
+    set_units(st, 0);
+    for (int u = max(u0, p.nF + p.n4 + p.n2); u < u1; ++u) {
+      const int win = (u - p.nF - p.n4 - p.n2) * kTR;
+      if (win >= rlen) continue;
       if (alive && !mbar_wait(&full_bar[stage], phase)) {
         if (lane == 0) atomicExch(p.err, R2K_ERR_DEVICE_TIMEOUT);
         alive = false;
       }
       if (alive) {
-        uint8_t* sb = stages + stage * kStageBytes;
-        if (tl.pool < 3) {
-          // INT4-/INT2-value tiles: 128 tokens, one key block per warp.  bf16-value tiles: 64 tokens = two key
-          // blocks; the lower half of the warps takes even tiles and the upper half odd ones, so every warp still works on 32 tokens at a
-          // time and pays the per-block work (Q' and the zero-point chain) once per 32 tokens.
-          constexpr int kHalf = kNW / 2;
-          const bool mine = tl.pool != 0 || ((u & 1) == (warp >= kHalf ? 1 : 0));
-          if (mine) {
-            const int r0 = tl.pool != 0 ? 32 * warp : 32 * (warp % kHalf);
-            const int lo = max(tl.lo - r0, 0), hi = min(tl.hi - r0, 32);
-            const int blk = ((tl.win + r0) >> p.kblock_shift) - (tl.win >> p.kblock_shift);
-            if (lo == 0 && hi == 32) consume_packed<false, BF16>(st, p, sb, tl.pool, r0, blk, lo, hi, qh, g, t, pg);
-            else if (hi > lo) consume_packed<true, BF16>(st, p, sb, tl.pool, r0, blk, lo, hi, qh, g, t, pg);
-          }
-        } else if (warp < 2) {
+        uint8_t* sbp = stages + stage * kStageBytes;
+        const uint32_t sb = stage0 + stage * kStageBytes;
+        if (warp < 2) {
           const int r0 = 16 * warp;
-          const int hi = min(rlen - tl.win - r0, 16);
+          const int hi = min(rlen - win - r0, 16);
           if (hi > 0) {
-            const int app_row = rlen0 - tl.win - r0;  // ring row that receives the appended token, relative to this slice
+            const int app_row = rlen0 - win - r0;  // ring row that receives the appended token, relative to this slice
             if (has_append && app_row >= 0 && app_row < 16) {
               const size_t off = ((size_t)b * p.g.num_kv_heads + h) * 256 + 8 * lane;
-              *reinterpret_cast<uint2*>(sb + kOffV + (r0 + app_row) * 256 + 8 * lane) =
+              *reinterpret_cast<uint2*>(sbp + kOffV + (r0 + app_row) * 256 + 8 * lane) =
                   __ldg(reinterpret_cast<const uint2*>((const uint8_t*)p.app_k + off));
-              *reinterpret_cast<uint2*>(sb + kOffV + kOffRecentV + (r0 + app_row) * 256 + 8 * lane) =
+              *reinterpret_cast<uint2*>(sbp + kOffV + kOffRecentV + (r0 + app_row) * 256 + 8 * lane) =
                   __ldg(reinterpret_cast<const uint2*>((const uint8_t*)p.app_v + off));
               __syncwarp();
             }
+            const int t0 = 2 * t + (t & 1), t1 = 2 * t + 1 - (t & 1);
             float s[1][4];
-            qk_fp<BF16>(sb + kOffV + r0 * 256, qrow, t, pg, p.qscale, s[0]);
+            qk_fp<BF16>(sb + kOffV + (r0 + pg) * 256 + 64 * t, qrow, t, p.qscale, s[0]);
             if (hi < 16) mask_scores(s[0], pg, 0, hi);
             softmax_update<1>(st, s);
-            set_units(st, 0);
-            pv_fp<BF16>(st, sb + kOffV + kOffRecentV + r0 * 256, s[0], g, t);
+            pv_fp<BF16>(st, sb, kOffV + kOffRecentV + (r0 + t0) * 256 + 32 * g, kOffV + kOffRecentV + (r0 + t1) * 256 + 32 * g, 0, s[0]);
           }
         }
         __syncwarp();

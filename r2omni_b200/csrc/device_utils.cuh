@@ -95,6 +95,16 @@ __device__ __forceinline__ bool mbar_wait(uint64_t* bar, uint32_t parity, uint32
   return false;
 }
 
+// The producer's wait: it is almost always early, so it sleeps between polls instead of spinning on the
+// issue slots of the scheduler it shares with two consumer warps.
+__device__ __forceinline__ bool mbar_wait_relaxed(uint64_t* bar, uint32_t parity, uint32_t limit = (1u << 20)) {
+  for (uint32_t i = 0; i < limit; ++i) {
+    if (mbar_try_wait(bar, parity)) return true;
+    __nanosleep(i < 4 ? 200 : 1000);
+  }
+  return false;
+}
+
 // 1-D bulk copy global -> shared (TMA), completion counted in bytes on `bar`.
 // Both addresses 16-byte aligned, bytes a multiple of 16.
 __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src, uint32_t bytes, uint64_t* bar) {
