@@ -106,6 +106,11 @@ class ClockSampler:
         return out
 
 
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode_kernel launch on the default workload, from the ncu
+# capture summarised in profiles/decode_kernel_b8_32k.md (96.55 MB read + 3.43 MB written, mean of two launches).
+NCU_DRAM_BYTES_PER_LAUNCH = 99_975_000
+
+
 def measured_peak_gbs():
     path = os.path.join(ROOT, "MEASURED_PEAKS.json")
     if os.path.exists(path):
@@ -452,7 +457,8 @@ def main():
     roofline = {"bound": "hbm", "kernel": "decode_kernel<bf16>", "achieved": round(achieved, 1), "peak": peak,
                 "peak_source": peak_kind, "unit": "GB/s", "frac": round(achieved / peak, 4),
                 "frac_of_nominal_8000": round(achieved / 8000.0, 4), "us_per_launch": round(k_ms * 1e3 / max(probe_steps, 1), 2),
-                "bytes_per_launch": int(k_bytes / max(probe_steps, 1)), "traffic": None}
+                "bytes_per_launch": int(k_bytes / max(probe_steps, 1)),
+                "traffic": NCU_DRAM_BYTES_PER_LAUNCH if args.workload == "decode_32k_b8" and args.page_mix == "25,50,25" else None}
 
     # end to end through the operator call with host buffers
     e2e = None
