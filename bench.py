@@ -176,6 +176,15 @@ class ReplicaBench:
             e.arenas.recent_len = ring
             self.step_graphs.append(gs)
             self.flush_graphs.append(gf)
+        # one graph per round (a step on every set, back to back): consecutive decode launches are joined by
+        # programmatic dependent launch edges, as consecutive layers of a model are
+        rings = [e.arenas.recent_len for e in self.ex]
+        self.round_graph = torch.cuda.CUDAGraph()
+        with torch.cuda.graph(self.round_graph):
+            for e in self.ex:
+                e(self.q, append=(self.k, self.v, tokens, tokens))
+        for e, ring in zip(self.ex, rings):
+            e.arenas.recent_len = ring
         self.launches_per_step = 1
         self.launches_per_flush = 3
         a = self.ex[0].arenas
@@ -188,16 +197,24 @@ class ReplicaBench:
     def run_graph_steps(self, steps, start=0):
         """Enqueue `steps` steps; returns (bytes moved, decode launches, flushes)."""
         total, flushes = 0, 0
-        for i in range(start, start + steps):
-            s = i % len(self.ex)
-            a = self.ex[s].arenas
-            if a.recent_len == RING:
-                self.flush_graphs[s].replay()
-                a.recent_len = 0
-                flushes += 1
-            total += self.step_bytes(a.recent_len + 1)
-            self.step_graphs[s].replay()
-            a.recent_len += 1
+        n, i, end = len(self.ex), start, start + steps
+        while i < end:
+            s = i % n
+            whole_round = s == 0 and i + n <= end
+            for t in (range(n) if whole_round else (s,)):
+                a = self.ex[t].arenas
+                if a.recent_len == RING:
+                    self.flush_graphs[t].replay()
+                    a.recent_len = 0
+                    flushes += 1
+                total += self.step_bytes(a.recent_len + 1)
+                a.recent_len += 1
+            if whole_round:
+                self.round_graph.replay()
+                i += n
+            else:
+                self.step_graphs[s].replay()
+                i += 1
         return total, steps, flushes
 
     def run_api_steps(self, steps, host_in, host_out, start=0):
@@ -434,29 +451,38 @@ def main():
 
     # the decode kernel alone: same graphs, no flush in the window
     probe_steps = 0
-    def decode_only():
+    def make_room():
+        for s, e in enumerate(bench.ex):
+            if e.arenas.recent_len > RING - 33:
+                bench.flush_graphs[s].replay()
+                e.arenas.recent_len = 0
+    def decode_only(rounds=True):
         nonlocal probe_steps
         b = 0
-        for i in range(32 * len(bench.ex)):
-            s = i % len(bench.ex)
-            a = bench.ex[s].arenas
-            if a.recent_len >= RING:
-                continue
-            b += bench.step_bytes(a.recent_len + 1)
-            bench.step_graphs[s].replay()
-            a.recent_len += 1
-            probe_steps += 1
+        for r in range(32):
+            for e in bench.ex:
+                b += bench.step_bytes(e.arenas.recent_len + 1)
+                e.arenas.recent_len += 1
+                probe_steps += 1
+            if rounds:
+                bench.round_graph.replay()
+            else:
+                for g in bench.step_graphs:
+                    g.replay()
         return b
-    for s, e in enumerate(bench.ex):   # make room in every ring first
-        if e.arenas.recent_len > RING - 33:
-            bench.flush_graphs[s].replay()
-            e.arenas.recent_len = 0
+    # launches separated by graph boundaries (no overlap between consecutive launches), for comparison
+    make_room()
+    iso_ms, _ = time_region(device, lambda: decode_only(False), dist_on)
+    iso_us = iso_ms * 1e3 / max(probe_steps, 1)
+    probe_steps = 0
+    make_room()
     k_ms, k_bytes = time_region(device, decode_only, dist_on)
     peak, peak_kind = measured_peak_gbs()
     achieved = k_bytes / (k_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "kernel": "decode_kernel<bf16>", "achieved": round(achieved, 1), "peak": peak,
                 "peak_source": peak_kind, "unit": "GB/s", "frac": round(achieved / peak, 4),
                 "frac_of_nominal_8000": round(achieved / 8000.0, 4), "us_per_launch": round(k_ms * 1e3 / max(probe_steps, 1), 2),
+                "us_per_launch_isolated": round(iso_us, 2),
                 "bytes_per_launch": int(k_bytes / max(probe_steps, 1)),
                 "traffic": NCU_DRAM_BYTES_PER_LAUNCH if args.workload == "decode_32k_b8" and args.page_mix == "25,50,25" else None}
 

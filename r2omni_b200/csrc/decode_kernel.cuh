@@ -390,6 +390,10 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const __gr
 
   const int warp = threadIdx.x >> 5, lane = threadIdx.x & 31;
   const int cta = blockIdx.x;
+  // The packed pools are never written by a decode launch, so the next decode of the stream may start streaming
+  // them as soon as SMs fall free.  Everything a previous kernel can have written (query, appended rows, residual
+  // window and its length, split-K workspace) is read only after grid_dependency_wait().
+  launch_dependents();
   if (threadIdx.x == 0) {
     for (int s = 0; s < kStages; ++s) { mbar_init(&full_bar[s], 1); mbar_init(&empty_bar[s], kNW); }
     mbar_fence_init();
@@ -417,9 +421,11 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const __gr
       for (int u = u0; u < u1; ++u) {
         const Tile tl = tile_of(p, u);
         if (tl.pool == 3) {
-          if (rlen < 0)
+          if (rlen < 0) {
+            grid_dependency_wait();   // the ring and its length belong to the previous step until it has completed
             rlen = *reinterpret_cast<const int*>((const uint8_t*)p.v.recent_len + (size_t)b * p.v.recent_len_bstride) +
                    (has_append ? 1 : 0);
+          }
           if (tl.win >= rlen) continue;
         }
         if (!mbar_wait_relaxed(&empty_bar[stage], phase ^ 1u)) {
@@ -444,6 +450,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const __gr
   const int g = lane >> 2, t = lane & 3, pg = pi_row(g);
   bool alive = true;
   WarpState st;
+  grid_dependency_wait();
 
   for (int bh = bh_lo; bh <= bh_hi; ++bh) {
     const int b = bh / p.g.num_kv_heads, h = bh - b * p.g.num_kv_heads;

@@ -118,4 +118,10 @@ __device__ __forceinline__ void named_bar_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;\n" ::"r"(id), "r"(threads) : "memory");
 }
 
+// Programmatic dependent launch.  launch_dependents lets the next kernel of the stream (when it was launched with
+// programmatic stream serialization) start its CTAs on SMs this grid has left; grid_dependency_wait blocks until
+// every kernel this grid depends on has completed and its writes are visible.  Both are no-ops otherwise.
+__device__ __forceinline__ void launch_dependents() { asm volatile("griddepcontrol.launch_dependents;" ::: "memory"); }
+__device__ __forceinline__ void grid_dependency_wait() { asm volatile("griddepcontrol.wait;" ::: "memory"); }
+
 }  // namespace r2k

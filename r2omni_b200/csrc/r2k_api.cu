@@ -1,6 +1,7 @@
 // extern "C" surface of libr2k_b200.so: validation, launch geometry, launches.
 // No torch types, no allocation, no synchronisation (except r2k_decode_device_status).
 #include <atomic>
+#include <cstdlib>
 #include <cstring>
 #include <mutex>
 
@@ -16,6 +17,7 @@ std::atomic<uint64_t> g_launches{0};
 struct DeviceInfo {
   int sms = 0;
   bool attr_set = false;
+  bool pdl = true;   // R2K_DISABLE_PDL=1 in the environment turns programmatic dependent launch off (debugging)
 };
 DeviceInfo g_dev[64];
 
@@ -27,6 +29,8 @@ int device_info(DeviceInfo** out) {
     int sms = 0;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) return R2K_ERR_CUDA;
     d.sms = sms;
+    const char* off = std::getenv("R2K_DISABLE_PDL");
+    d.pdl = !(off != nullptr && off[0] == '1');
   }
   *out = &d;
   return R2K_OK;
@@ -266,12 +270,23 @@ int r2k_decode(const R2KGeom* geom, const R2KCacheView* view, const void* q, con
     dev->attr_set = true;
   }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
-  if (geom->dtype == R2K_DTYPE_BF16)
-    decode_kernel<true><<<p.grid, kThreads, kSmemBytes, st>>>(p);
-  else
-    decode_kernel<false><<<p.grid, kThreads, kSmemBytes, st>>>(p);
+  // Programmatic stream serialization: when the previous kernel of the stream signals early (a decode launch
+  // does), this grid's CTAs may start on free SMs and prefetch pool tiles; the kernel itself waits for the
+  // previous kernel's completion before it reads anything that kernel can have written.
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = dev->pdl ? 1 : 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = dim3((unsigned)p.grid);
+  cfg.blockDim = dim3(kThreads);
+  cfg.dynamicSmemBytes = kSmemBytes;
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  const cudaError_t err = geom->dtype == R2K_DTYPE_BF16 ? cudaLaunchKernelEx(&cfg, decode_kernel<true>, p)
+                                                        : cudaLaunchKernelEx(&cfg, decode_kernel<false>, p);
   ++g_launches;
-  return cudaGetLastError() == cudaSuccess ? R2K_OK : R2K_ERR_CUDA;
+  return err == cudaSuccess ? R2K_OK : R2K_ERR_CUDA;
 }
 
 }  // extern "C"
