@@ -131,7 +131,7 @@ struct LaneOffsets {
 
 // Scores of two 16-token tiles against INT4 keys.  Q' = q * scale is held as an exact two-term fp16 sum
 // (hi = RN(q*s), lo = fma(q, s, -hi)), so every product the tensor core sees is exact and the fp32
-// accumulation is the only rounding.  Codes are fed as fp16 subnormals straight out of an AND.
+// accumulation is the only rounding.  Codes minus zero points are fed as signed fp16 subnormals (AND, HSUB2).
 __device__ __forceinline__ void qk_int4(uint32_t sb, const LaneOffsets& o, const uint32_t (&qh)[16], float alpha,
                                         float (&s)[2][4]) {
   uint32_t qp[16], ql[16];  // paired (c0,c4) (c1,c5) (c2,c6) (c3,c7) per 8-channel word
@@ -146,26 +146,20 @@ __device__ __forceinline__ void qk_int4(uint32_t sb, const LaneOffsets& o, const
       ql[4 * i + k] = hfma2_neg_u32(qh[4 * i + k], sp[k], qp[4 * i + k]);
     }
   }
-  // zero-point term sum_c Q'[c] * zero[c]: one more MMA chain whose 16 rows are all the zero row
-  float zc[4];
+  // Zero points as fp16 subnormal pairs in the two code domains: (z0,z4), (z2,z6) scaled 2^-24 for the low
+  // nibbles and (z1,z5), (z3,z7) scaled 2^-20 for the high ones.  code - zero is then one exact HSUB2 per
+  // register (subnormal arithmetic is exact on integers), and the tensor core sees signed integers.
+  uint32_t zl[8], zh[8];
   {
-    float zq[4][4];
     const uint4 za = lds128(sb + o.kz), zb = lds128(sb + o.kz + 16);
     const uint32_t z[8] = {za.x, za.y, za.z, za.w, zb.x, zb.y, zb.z, zb.w};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const uint32_t x = __byte_perm(z[2 * i], z[2 * i + 1], 0x5410);  // z0 z1 z4 z5
       const uint32_t y = __byte_perm(z[2 * i], z[2 * i + 1], 0x7632);  // z2 z3 z6 z7
-      const uint32_t r0 = x & 0x00FF00FFu, r1 = __byte_perm(x, 0u, 0x4341);
-      const uint32_t r2 = y & 0x00FF00FFu, r3 = __byte_perm(y, 0u, 0x4341);
-      zq[i][0] = zq[i][1] = zq[i][2] = zq[i][3] = 0.f;   // four independent chains
-      mma_f16(zq[i], r0, r0, r2, r2, qp[4 * i + 0], qp[4 * i + 2]);
-      mma_f16(zq[i], r1, r1, r3, r3, qp[4 * i + 1], qp[4 * i + 3]);
-      mma_f16(zq[i], r0, r0, r2, r2, ql[4 * i + 0], ql[4 * i + 2]);
-      mma_f16(zq[i], r1, r1, r3, r3, ql[4 * i + 1], ql[4 * i + 3]);
+      zl[2 * i] = x & 0x00FF00FFu;     zh[2 * i] = (x >> 4) & 0x0FF00FF0u;
+      zl[2 * i + 1] = y & 0x00FF00FFu; zh[2 * i + 1] = (y >> 4) & 0x0FF00FF0u;
     }
-#pragma unroll
-    for (int c = 0; c < 4; ++c) zc[c] = (zq[0][c] + zq[1][c]) + (zq[2][c] + zq[3][c]);
   }
   const float f24 = k2p24 * alpha, f20 = k2p20 * alpha;
 #pragma unroll
@@ -173,12 +167,14 @@ __device__ __forceinline__ void qk_int4(uint32_t sb, const LaneOffsets& o, const
     const uint4 ka = lds128(sb + o.k + 16 * j * 64);
     const uint4 kb = lds128(sb + o.k + (16 * j + 8) * 64);
     const uint32_t wa[4] = {ka.x, ka.y, ka.z, ka.w}, wb[4] = {kb.x, kb.y, kb.z, kb.w};
-    float lo[4] = {-zc[0], -zc[1], -zc[2], -zc[3]}, hi[4] = {0.f, 0.f, 0.f, 0.f};
+    float lo[4] = {0.f, 0.f, 0.f, 0.f}, hi[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
       const uint32_t a8 = wa[i] >> 8, b8 = wb[i] >> 8;
-      const uint32_t l0 = wa[i] & kMaskLo, l1 = wb[i] & kMaskLo, l2 = a8 & kMaskLo, l3 = b8 & kMaskLo;
-      const uint32_t h0 = wa[i] & kMaskHi, h1 = wb[i] & kMaskHi, h2 = a8 & kMaskHi, h3 = b8 & kMaskHi;
+      const uint32_t l0 = hsub2_u32(wa[i] & kMaskLo, zl[2 * i]), l1 = hsub2_u32(wb[i] & kMaskLo, zl[2 * i]);
+      const uint32_t l2 = hsub2_u32(a8 & kMaskLo, zl[2 * i + 1]), l3 = hsub2_u32(b8 & kMaskLo, zl[2 * i + 1]);
+      const uint32_t h0 = hsub2_u32(wa[i] & kMaskHi, zh[2 * i]), h1 = hsub2_u32(wb[i] & kMaskHi, zh[2 * i]);
+      const uint32_t h2 = hsub2_u32(a8 & kMaskHi, zh[2 * i + 1]), h3 = hsub2_u32(b8 & kMaskHi, zh[2 * i + 1]);
       mma_f16(lo, l0, l1, l2, l3, qp[4 * i + 0], qp[4 * i + 2]);
       mma_f16(hi, h0, h1, h2, h3, qp[4 * i + 1], qp[4 * i + 3]);
       mma_f16(lo, l0, l1, l2, l3, ql[4 * i + 0], ql[4 * i + 2]);
