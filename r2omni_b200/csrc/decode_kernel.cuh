@@ -546,6 +546,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const __gr
     const int part0 = first_cta_of(p, bh);
     const int nparts = last_cta_of(p, bh) - part0 + 1;
     float* slot = p.partials + ((size_t)bh * p.parts_cap + (cta - part0)) * kSlotFloats;
+    static_assert(kNW >= 6, "warps 4 and 5 carry the request counter and the appended rows");
     const bool worker = threadIdx.x < 128;   // warps 0-3 carry the merge protocol; the others only meet the barriers
     if (worker) {
       const int hh = threadIdx.x >> 4, sub = threadIdx.x & 15;  // 16 threads per head, 8 dims each
@@ -605,20 +606,13 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const __gr
     }
     if (last) {
       // ---- last arriver of (b, h): epilogue and fused append ----
-      if (worker) write_output<BF16>(p, (size_t)b * p.g.num_q_heads + h * p.gqa + hh, hh < p.gqa, sub, mx, lsum, acc);
-      if (has_append && warp == 0) {  // ring row rlen0 of head h
-        const size_t src = ((size_t)b * p.g.num_kv_heads + h) * 256 + 8 * lane;
-        const size_t dst = ((size_t)h * p.g.recent_capacity + rlen0) * 256 + 8 * lane;
-        *reinterpret_cast<uint2*>((uint8_t*)p.v.recent_k + (size_t)b * p.v.recent_k_bstride + dst) =
-            __ldg(reinterpret_cast<const uint2*>((const uint8_t*)p.app_k + src));
-        *reinterpret_cast<uint2*>((uint8_t*)p.v.recent_v + (size_t)b * p.v.recent_v_bstride + dst) =
-            __ldg(reinterpret_cast<const uint2*>((const uint8_t*)p.app_v + src));
-      }
-      named_bar_sync(1, kConsumers);
-      if (threadIdx.x == 0) {
+      // Every CTA of this head has arrived, so none of them reads recent_len[b] any more.  One thread outside
+      // the merge workers counts the head in; the last head of the request moves the ring metadata.  This runs
+      // beside the merge below, not after it.
+      if (threadIdx.x == 128) {
         __threadfence();
         const int done = atomicAdd(&p.req_counter[b], 1);
-        if (done == p.g.num_kv_heads - 1) {  // every head of request b is merged: nobody reads recent_len[b] any more
+        if (done == p.g.num_kv_heads - 1) {
           p.req_counter[b] = 0;
           if (has_append) {
             const int64_t gi = p.app_idx ? p.app_idx[2 * b] : p.app_global;
@@ -631,6 +625,15 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const __gr
           }
         }
       }
+      if (has_append && warp == 5) {  // ring row rlen0 of head h
+        const size_t src = ((size_t)b * p.g.num_kv_heads + h) * 256 + 8 * lane;
+        const size_t dst = ((size_t)h * p.g.recent_capacity + rlen0) * 256 + 8 * lane;
+        *reinterpret_cast<uint2*>((uint8_t*)p.v.recent_k + (size_t)b * p.v.recent_k_bstride + dst) =
+            __ldg(reinterpret_cast<const uint2*>((const uint8_t*)p.app_k + src));
+        *reinterpret_cast<uint2*>((uint8_t*)p.v.recent_v + (size_t)b * p.v.recent_v_bstride + dst) =
+            __ldg(reinterpret_cast<const uint2*>((const uint8_t*)p.app_v + src));
+      }
+      if (worker) write_output<BF16>(p, (size_t)b * p.g.num_q_heads + h * p.gqa + hh, hh < p.gqa, sub, mx, lsum, acc);
     }
     named_bar_sync(1, kConsumers);  // scratch and flags are reused by the next (request, kv head)
   }
