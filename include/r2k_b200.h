@@ -230,6 +230,14 @@ int r2k_pack_v_int2(const void* src, int32_t dtype, int32_t num_kv_heads, int64_
 int r2k_gather_rows(const void* src, int32_t num_kv_heads, int64_t src_rows, const int64_t* index,
                     int64_t count, void* dst, int64_t dst_rows, int64_t dst_start, void* stream);
 
+/* Normalised 128-point Walsh-Hadamard transform of `rows` 128-wide rows of the
+ * given 16-bit type (fp32 butterflies, stages of stride 1..64, times 128^-1/2,
+ * rounded to the element type); in place when out == in.  Replaces
+ * triton_fwht_128 / _fwht_128_kernel (r2omni/sspa/kernels/triton_qwen_mrope.py:
+ * 13-42, 325-346; CPU form normalized_fwht, r2omni/sspa/runtime/int2_reference.py:18-31):
+ * the pre-conditioning of new key/value rows when key_hadamard / value_hadamard is on. */
+int r2k_fwht128(const void* in, void* out, int32_t dtype, int64_t rows, void* stream);
+
 /* ---- residual window ---------------------------------------------------- */
 
 /*

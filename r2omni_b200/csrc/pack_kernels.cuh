@@ -246,4 +246,47 @@ __global__ void flush_ring_kernel(RingArgs r, int ring_tokens, int flush_tokens,
   }
 }
 
+// ---------------------------------------------------------------------------
+// Normalised 128-point Walsh-Hadamard transform of 16-bit rows, fp32 butterflies in the reference's stage order
+// (stride 1, 2, ..., 64), result rounded to the element type.  One warp per row, four consecutive channels per
+// lane: two stages in registers, five through shuffles.  In place when out == in.
+// ---------------------------------------------------------------------------
+template <bool BF16>
+__global__ void fwht128_kernel(const uint16_t* __restrict__ in, uint16_t* __restrict__ out, int64_t rows) {
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  if (row >= rows) return;
+  const uint2 raw = *reinterpret_cast<const uint2*>(in + row * 128 + 4 * lane);
+  float r[4];
+  if (BF16) {
+    r[0] = __uint_as_float(raw.x << 16); r[1] = __uint_as_float(raw.x & 0xffff0000u);
+    r[2] = __uint_as_float(raw.y << 16); r[3] = __uint_as_float(raw.y & 0xffff0000u);
+  } else {
+    const float2 a = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+    const float2 b = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+    r[0] = a.x; r[1] = a.y; r[2] = b.x; r[3] = b.y;
+  }
+  const float a = __fadd_rn(r[0], r[1]), b = __fsub_rn(r[0], r[1]), c = __fadd_rn(r[2], r[3]), d = __fsub_rn(r[2], r[3]);
+  r[0] = __fadd_rn(a, c); r[1] = __fadd_rn(b, d); r[2] = __fsub_rn(a, c); r[3] = __fsub_rn(b, d);
+#pragma unroll
+  for (int sft = 1; sft < 32; sft <<= 1) {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const float o = __shfl_xor_sync(0xffffffffu, r[e], sft);
+      r[e] = (lane & sft) ? __fsub_rn(o, r[e]) : __fadd_rn(r[e], o);
+    }
+  }
+#pragma unroll
+  for (int e = 0; e < 4; ++e) r[e] = __fmul_rn(r[e], 0.08838834764831845f);
+  uint2 pk;
+  if (BF16) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(r[0], r[1]), hi = __floats2bfloat162_rn(r[2], r[3]);
+    pk.x = *reinterpret_cast<uint32_t*>(&lo); pk.y = *reinterpret_cast<uint32_t*>(&hi);
+  } else {
+    __half2 lo = __floats2half2_rn(r[0], r[1]), hi = __floats2half2_rn(r[2], r[3]);
+    pk.x = *reinterpret_cast<uint32_t*>(&lo); pk.y = *reinterpret_cast<uint32_t*>(&hi);
+  }
+  *reinterpret_cast<uint2*>(out + row * 128 + 4 * lane) = pk;
+}
+
 }  // namespace r2k

@@ -410,6 +410,21 @@ int r2k_gather_rows(const void* src, int32_t num_kv_heads, int64_t src_rows, con
   return cudaGetLastError() == cudaSuccess ? R2K_OK : R2K_ERR_CUDA;
 }
 
+int r2k_fwht128(const void* in, void* out, int32_t dtype, int64_t rows, void* stream) {
+  if (in == nullptr || out == nullptr) return R2K_ERR_NULL;
+  if (rows < 0 || (dtype != R2K_DTYPE_BF16 && dtype != R2K_DTYPE_FP16)) return R2K_ERR_GEOMETRY;
+  if ((reinterpret_cast<uintptr_t>(in) | reinterpret_cast<uintptr_t>(out)) & 7u) return R2K_ERR_ALIGNMENT;
+  if (rows == 0) return R2K_OK;
+  const unsigned grid = (unsigned)((rows + 3) / 4);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == R2K_DTYPE_BF16)
+    fwht128_kernel<true><<<grid, 128, 0, st>>>(reinterpret_cast<const uint16_t*>(in), reinterpret_cast<uint16_t*>(out), rows);
+  else
+    fwht128_kernel<false><<<grid, 128, 0, st>>>(reinterpret_cast<const uint16_t*>(in), reinterpret_cast<uint16_t*>(out), rows);
+  ++g_launches;
+  return cudaGetLastError() == cudaSuccess ? R2K_OK : R2K_ERR_CUDA;
+}
+
 int r2k_append_recent(const R2KGeom* geom, const R2KCacheView* view, const R2KAppend* append, void* stream) {
   if (view == nullptr || append == nullptr || append->k == nullptr || append->v == nullptr) return R2K_ERR_NULL;
   int rc = check_geom(geom);
