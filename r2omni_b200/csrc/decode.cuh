@@ -1,6 +1,7 @@
 // Geometry shared by the host launcher and the decode kernel.
 #pragma once
 
+#include <cuda.h>
 #include <stdint.h>
 
 #include "r2k_b200.h"
@@ -27,6 +28,9 @@ constexpr int kStageBytes = kOffKZ + (kTQ / 32) * 128;
 static_assert(kStageBytes % 128 == 0, "stage must stay 128-byte aligned");
 static_assert(kTF % 128 == 0 && kTQ % 128 == 0, "tile windows must start on multiples of the largest key block");
 // value region, per pool
+// bf16-value tiles are stored as two half boxes (channels 0-63, 64-127) of kTF rows x 128 bytes; inside every
+// row the 16-byte chunks are XOR-swizzled by (row & 7) -- the layout of a 128-byte-swizzled tensor copy.
+constexpr int kFpHalfBytes = kTF * 128;
 constexpr int kOffI4Scale = kTQ * 64;            // f32 per token after the nibble rows
 constexpr int kOffI2Scale = kTQ * 32;            // f16 x groups per token after the crumb rows
 constexpr int kOffI2Zero = kOffI2Scale + kTQ * 8;
@@ -65,6 +69,10 @@ struct DecodeParams {
   uint32_t cF, c4, c2, cR, c_bh;  // tile cost weights and their sum per (request, kv head); c_bh < 2^22
   int groups2, group2_shift, kblock_shift;
   float qscale;                   // sm_scale * log2(e)
+  // bf16-value pool as a 4-D tensor {128, fp_capacity, kv heads, requests} with 64-element boxes and 128-byte
+  // swizzle: full value tiles arrive bank-conflict-free for the value MMA's loads (valid when fp_tma != 0)
+  int fp_tma;
+  alignas(64) CUtensorMap fp_map;
 };
 
 // Work is laid out on a cost axis: (request, kv head) bh owns [bh*c_bh, (bh+1)*c_bh), a tile owns its cost

@@ -118,6 +118,13 @@ __device__ __forceinline__ void mask_scores(float (&s)[4], int row_a, int lo, in
   if (row_a + 8 < lo || row_a + 8 >= hi) s[2] = s[3] = -INFINITY;
 }
 
+// Byte offset, inside the value region of a bf16-value tile, of 16-byte chunk c (0..15) of row r: half box
+// c / 8, row pitch 128 bytes, chunk index XOR (r & 7).  This is where a 128-byte-swizzled tensor copy of the two
+// 64-channel boxes puts it (the region is 1024-byte aligned), and what the plain-load path reproduces.
+__host__ __device__ __forceinline__ uint32_t fp_box_offset(int r, int c) {
+  return (uint32_t)((c >> 3) * kFpHalfBytes + r * 128 + (((c & 7) ^ (r & 7)) * 16));
+}
+
 // Per-lane shared-memory offsets (relative to the stage base) of one warp's 32-token slice.
 struct LaneOffsets {
   uint32_t k;    // key rows: (slice + pi(g)) * 64 + 16 t        (+ (16 j + 8 e) * 64)
@@ -277,8 +284,12 @@ __device__ __forceinline__ void pv_int2(WarpState& st, uint32_t sb, const LaneOf
 
 // O^T += V^T P^T for 16-token tile j of 16-bit values (rows of 256 bytes): prmt pair-transposes; for bf16 the
 // probabilities go in as two bf16 terms (P = P_hi + P_lo, two MMAs) to keep ~16 mantissa bits of P.
-template <bool BF16>
+// SWZ: rows of a swizzled half box (128-byte pitch, see fp_box_offset): va / vb carry the swizzled offset of the
+// lane's first 16-byte chunk and the second chunk is its neighbour (offset ^ 16).  Plain 256-byte rows (the
+// residual window) cost a 4-way bank conflict on every load here, which does not matter for 32 tokens.
+template <bool BF16, bool SWZ>
 __device__ __forceinline__ void pv_fp(WarpState& st, uint32_t sb, uint32_t va, uint32_t vb, int j, float (&pr)[4]) {
+  constexpr int kPitch = SWZ ? 128 : 256;
   uint32_t bh0, bh1, bl0 = 0, bl1 = 0;
   if (BF16) {
     const uint32_t ha = pack_bf16x2(pr[0], pr[1]), hb = pack_bf16x2(pr[2], pr[3]);
@@ -291,8 +302,10 @@ __device__ __forceinline__ void pv_fp(WarpState& st, uint32_t sb, uint32_t va, u
   }
 #pragma unroll
   for (int hf = 0; hf < 2; ++hf) {
-    const uint4 r0 = lds128(sb + va + 4096 * j + 16 * hf), r1 = lds128(sb + vb + 4096 * j + 16 * hf);
-    const uint4 r2 = lds128(sb + va + 4096 * j + 2048 + 16 * hf), r3 = lds128(sb + vb + 4096 * j + 2048 + 16 * hf);
+    const uint32_t xa = SWZ ? ((va + 16 * kPitch * j) ^ (16 * hf)) : (va + 16 * kPitch * j + 16 * hf);
+    const uint32_t xb = SWZ ? ((vb + 16 * kPitch * j) ^ (16 * hf)) : (vb + 16 * kPitch * j + 16 * hf);
+    const uint4 r0 = lds128(sb + xa), r1 = lds128(sb + xb);
+    const uint4 r2 = lds128(sb + xa + 8 * kPitch), r3 = lds128(sb + xb + 8 * kPitch);
     const uint32_t a[4] = {r0.x, r0.y, r0.z, r0.w}, b[4] = {r1.x, r1.y, r1.z, r1.w};
     const uint32_t c[4] = {r2.x, r2.y, r2.z, r2.w}, d[4] = {r3.x, r3.y, r3.z, r3.w};
 #pragma unroll

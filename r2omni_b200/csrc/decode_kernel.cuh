@@ -89,6 +89,22 @@ __device__ __forceinline__ void zero_piece(uint8_t* dst, int bytes, int lane) {
   for (int i = lane; i < bytes; i += 32) dst[i] = 0;
 }
 
+// Rows [lo, hi) of a bf16-value tile written into the swizzled half boxes by plain loads (ragged tiles, unaligned
+// pools): `src` addresses row lo.  Rows outside [lo, hi) are cleared, so a masked row never feeds a NaN.
+__device__ __forceinline__ void copy_fp_rows(uint8_t* vreg, const uint8_t* src, int lo, int hi, int len, int lane) {
+  const int chunks = (hi - lo) * 16;
+  if ((reinterpret_cast<uintptr_t>(src) & 15u) == 0) {
+    for (int i = lane; i < chunks; i += 32)
+      *reinterpret_cast<uint4*>(vreg + fp_box_offset(lo + (i >> 4), i & 15)) = __ldg(reinterpret_cast<const uint4*>(src) + i);
+  } else {
+    for (int i = lane; i < chunks * 16; i += 32) vreg[fp_box_offset(lo + (i >> 8), (i >> 4) & 15) + (i & 15)] = src[i];
+  }
+  for (int half = 0; half < 2; ++half) {
+    zero_piece(vreg + half * kFpHalfBytes, lo * 128, lane);
+    zero_piece(vreg + half * kFpHalfBytes + hi * 128, (len - hi) * 128, lane);
+  }
+}
+
 __device__ __forceinline__ void produce_tile(const DecodeParams& p, const Tile& tl, int b, int h, uint8_t* stage,
                                              uint64_t* bar, int lane) {
   uint32_t tx = 0;
@@ -118,8 +134,7 @@ __device__ __forceinline__ void produce_tile(const DecodeParams& p, const Tile& 
     uint8_t* vreg = stage + kOffV;
     if (tl.pool == 0) {
       const size_t row = (size_t)h * p.g.fp_capacity + (tl.win + tl.lo - p.g.k_off_fp);
-      copy_piece(vreg + tl.lo * 256, (const uint8_t*)v.fp_v + (size_t)b * v.fp_v_bstride + row * 256, nvalid * 256, bar, lane, tx);
-      if (nvalid < len) { zero_piece(vreg, tl.lo * 256, lane); zero_piece(vreg + tl.hi * 256, (len - tl.hi) * 256, lane); }
+      copy_fp_rows(vreg, (const uint8_t*)v.fp_v + (size_t)b * v.fp_v_bstride + row * 256, tl.lo, tl.hi, len, lane);
     } else if (tl.pool == 1) {
       const size_t row = (size_t)h * p.g.i4_capacity + (tl.win + tl.lo - p.g.k_off_i4);
       copy_piece(vreg + tl.lo * 64, v.i4_packed + (size_t)b * v.i4_packed_bstride + row * 64, nvalid * 64, bar, lane, tx);
@@ -153,7 +168,7 @@ struct TileSources {
   const uint8_t* s1;       // INT4-value scales
   const uint8_t* s2;       // INT2-value scales
   const uint8_t* z2;       // INT2-value zero points
-  bool fast0, fast1, fast2; // every full tile of the pool can go through 16-byte-aligned bulk copies
+  bool fast1, fast2;       // every full tile of the pool can go through 16-byte-aligned bulk copies
 };
 
 __device__ __forceinline__ TileSources tile_sources(const DecodeParams& p, int b, int h) {
@@ -172,15 +187,14 @@ __device__ __forceinline__ TileSources tile_sources(const DecodeParams& p, int b
   s.s2 = (const uint8_t*)v.i2_scale + (int64_t)b * v.i2_scale_bstride + r2 * p.groups2 * 2;
   s.z2 = v.i2_zero + (int64_t)b * v.i2_zero_bstride + r2 * p.groups2;
   // full tiles start at multiples of 64 rows, so base alignment decides everything
-  s.fast0 = (((uintptr_t)s.v0) & 15) == 0;
   s.fast1 = ((((uintptr_t)s.v1) | ((uintptr_t)s.s1)) & 15) == 0;
   s.fast2 = ((((uintptr_t)s.v2) | ((uintptr_t)s.s2) | ((uintptr_t)s.z2)) & 15) == 0 && p.groups2 == 4;
   return s;
 }
 
 // A full, aligned tile: one lane issues the bulk copies; no per-lane work, no 64-bit multiplies.
-__device__ __forceinline__ void produce_full_tile(const DecodeParams& p, const TileSources& src, int pool, int win,
-                                                  uint8_t* stage, uint64_t* bar) {
+__device__ __forceinline__ void produce_full_tile(const DecodeParams& p, const TileSources& src, int pool, int win, int b,
+                                                  int h, uint8_t* stage, uint64_t* bar) {
   const int len = pool == 0 ? kTF : kTQ;
   const int nblk = max(1, len >> p.kblock_shift);
   const int blk0 = win >> p.kblock_shift;
@@ -190,8 +204,10 @@ __device__ __forceinline__ void produce_full_tile(const DecodeParams& p, const T
   bulk_g2s(stage + kOffK, src.kp + (size_t)win * 64, (uint32_t)(len * 64), bar);
   bulk_g2s(stage + kOffKS, src.ks + (size_t)blk0 * 256, (uint32_t)(nblk * 256), bar);
   bulk_g2s(stage + kOffKZ, src.kz + (size_t)blk0 * 128, (uint32_t)(nblk * 128), bar);
-  if (pool == 0) {
-    bulk_g2s(stage + kOffV, src.v0 + (size_t)win * 256, (uint32_t)(len * 256), bar);
+  if (pool == 0) {   // two 64-channel boxes of kTF rows, 128-byte swizzle
+    const int row = win - p.g.k_off_fp;
+    tensor_g2s_4d(stage + kOffV, &p.fp_map, 0, row, h, b, bar);
+    tensor_g2s_4d(stage + kOffV + kFpHalfBytes, &p.fp_map, 64, row, h, b, bar);
   } else if (pool == 1) {
     bulk_g2s(stage + kOffV, src.v1 + (size_t)win * 64, (uint32_t)(len * 64), bar);
     bulk_g2s(stage + kOffV + kOffI4Scale, src.s1 + (size_t)win * 4, (uint32_t)(len * 4), bar);
@@ -312,7 +328,7 @@ __device__ __forceinline__ void consume_block(WarpState& st, uint32_t sb, const 
   softmax_update<2>(st, s);
 #pragma unroll
   for (int j = 0; j < 2; ++j) {
-    if (POOL == 0) pv_fp<BF16>(st, sb, o.va, o.vb, j, s[j]);
+    if (POOL == 0) pv_fp<BF16, true>(st, sb, o.va, o.vb, j, s[j]);
     else if (POOL == 1) pv_int4<PARTIAL>(st, sb, o, j, s[j], pg, lo, hi);
     else pv_int2<PARTIAL>(st, sb, o, j, s[j], t, step, lo, hi);
   }
@@ -342,7 +358,9 @@ __device__ __forceinline__ void consume_pool(WarpState& st, const DecodeParams& 
   o.kz = kOffKZ + blk * 128 + 32 * t;
   int step = 0;
   if (POOL == 0) {
-    o.va = kOffV + (slice + t0) * 256 + 32 * g; o.vb = kOffV + (slice + t1) * 256 + 32 * g; o.m0 = o.m1 = 0;
+    o.va = kOffV + fp_box_offset(slice + t0, 2 * g);   // swizzled half boxes
+    o.vb = kOffV + fp_box_offset(slice + t1, 2 * g);
+    o.m0 = o.m1 = 0;
   } else if (POOL == 1) {
     o.va = kOffV + (slice + t0) * 64 + 8 * g; o.vb = kOffV + (slice + t1) * 64 + 8 * g;
     o.m0 = kOffV + kOffI4Scale + (slice + pg) * 4; o.m1 = 0;
@@ -434,9 +452,10 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const __gr
           break;
         }
         uint8_t* sb = stages + stage * kStageBytes;
-        const bool full = tl.pool < 3 && tl.lo == 0 && tl.hi == (tl.pool == 0 ? kTF : kTQ) && (tl.pool == 0 ? src.fast0 : tl.pool == 1 ? src.fast1 : src.fast2);
+        const bool full = tl.pool < 3 && tl.lo == 0 && tl.hi == (tl.pool == 0 ? kTF : kTQ) &&
+                          (tl.pool == 0 ? p.fp_tma != 0 : tl.pool == 1 ? src.fast1 : src.fast2);
         if (full) {
-          if (lane == 0) produce_full_tile(p, src, tl.pool, tl.win, sb, &full_bar[stage]);
+          if (lane == 0) produce_full_tile(p, src, tl.pool, tl.win, b, h, sb, &full_bar[stage]);
         } else {
           produce_tile(p, tl, b, h, sb, &full_bar[stage], lane);
         }
@@ -512,7 +531,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const __gr
             qk_fp<BF16>(sb + kOffV + (r0 + pg) * 256 + 64 * t, qrow, t, p.qscale, s[0]);
             if (hi < 16) mask_scores(s[0], pg, 0, hi);
             softmax_update<1>(st, s);
-            pv_fp<BF16>(st, sb, kOffV + kOffRecentV + (r0 + t0) * 256 + 32 * g, kOffV + kOffRecentV + (r0 + t1) * 256 + 32 * g, 0, s[0]);
+            pv_fp<BF16, false>(st, sb, kOffV + kOffRecentV + (r0 + t0) * 256 + 32 * g, kOffV + kOffRecentV + (r0 + t1) * 256 + 32 * g, 0,
+                               s[0]);
           }
         }
         __syncwarp();

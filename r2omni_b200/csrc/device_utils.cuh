@@ -114,6 +114,16 @@ __device__ __forceinline__ void bulk_g2s(void* dst_smem, const void* src, uint32
                : "memory");
 }
 
+// Tiled 4-D tensor copy global -> shared (TMA) of one box at coordinates {x, y, z, w}; x * element size must be
+// a multiple of 16 bytes.  Completion is counted in bytes on `bar`.
+__device__ __forceinline__ void tensor_g2s_4d(void* dst_smem, const void* tmap, int x, int y, int z, int w, uint64_t* bar) {
+  asm volatile(
+      "cp.async.bulk.tensor.4d.shared::cluster.global.tile.mbarrier::complete_tx::bytes [%0], [%1, {%2, %3, %4, %5}], [%6];\n" ::"r"(
+          smem_u32(dst_smem)),
+      "l"(tmap), "r"(x), "r"(y), "r"(z), "r"(w), "r"(smem_u32(bar))
+      : "memory");
+}
+
 __device__ __forceinline__ void named_bar_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;\n" ::"r"(id), "r"(threads) : "memory");
 }

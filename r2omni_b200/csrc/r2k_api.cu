@@ -83,7 +83,7 @@ int derive(const R2KGeom* g, DecodeParams* p) {
   // are measured per-tile times (ns of one CTA slot on B200, pure-pool caches), scaled down until a whole
   // (request, kv head) fits in 22 bits: the kernel's partition arithmetic is 32-bit.
   (void)g2;
-  const double ns[4] = {1650.0, 2540.0, 2850.0, 900.0};
+  const double ns[4] = {1290.0, 2110.0, 2310.0, 450.0};
   const int64_t cnt[4] = {p->nF, p->n4, p->n2, p->nR};
   double scale = 100.0;
   uint32_t w[4];
@@ -122,6 +122,65 @@ size_t counters_bytes(const DecodeParams& p) {
 size_t workspace_need(const DecodeParams& p) {
   return kWsHeaderBytes + counters_bytes(p) +
          (size_t)p.bh_total * (p.parts_cap + p.groups_cap) * kSlotFloats * sizeof(float);
+}
+
+// ---- tensor map of the bf16-value pool -------------------------------------------------------------------
+// Encoded through the driver entry point (no link against the driver library); the last few maps are kept,
+// keyed by everything that goes into them, because callers decode with the same cache many times.
+using EncodeTiledFn = CUresult (*)(CUtensorMap*, CUtensorMapDataType, cuuint32_t, void*, const cuuint64_t*, const cuuint64_t*,
+                                   const cuuint32_t*, const cuuint32_t*, CUtensorMapInterleave, CUtensorMapSwizzle,
+                                   CUtensorMapL2promotion, CUtensorMapFloatOOBfill);
+struct FpMapKey {
+  const void* base; int64_t bstride; int32_t capacity, heads, batch;
+  bool operator==(const FpMapKey& o) const {
+    return base == o.base && bstride == o.bstride && capacity == o.capacity && heads == o.heads && batch == o.batch;
+  }
+};
+struct FpMapEntry { FpMapKey key; CUtensorMap map; bool used = false; };
+std::mutex g_map_mutex;
+FpMapEntry g_maps[8];
+int g_map_next = 0;
+
+EncodeTiledFn encode_tiled_fn() {
+  static EncodeTiledFn fn = [] {
+    void* sym = nullptr;
+    cudaDriverEntryPointQueryResult res;
+    if (cudaGetDriverEntryPoint("cuTensorMapEncodeTiled", &sym, cudaEnableDefault, &res) != cudaSuccess ||
+        res != cudaDriverEntryPointSuccess)
+      sym = nullptr;
+    return reinterpret_cast<EncodeTiledFn>(sym);
+  }();
+  return fn;
+}
+
+// Fills p->fp_map / p->fp_tma.  Any reason the map cannot be built (no pool, unaligned base or stride, no driver
+// entry point) leaves fp_tma = 0 and the kernel on its plain-load path for bf16-value tiles.
+void bind_fp_map(DecodeParams* p) {
+  p->fp_tma = 0;
+  const R2KGeom& g = p->g;
+  if (g.n_fp <= 0 || g.fp_capacity <= 0 || p->v.fp_v == nullptr) return;
+  const int64_t bstride = g.batch > 1 ? p->v.fp_v_bstride : (int64_t)g.fp_capacity * g.num_kv_heads * 256;
+  if ((reinterpret_cast<uintptr_t>(p->v.fp_v) & 15u) || bstride <= 0 || (bstride & 15)) return;
+  EncodeTiledFn encode = encode_tiled_fn();
+  if (encode == nullptr) return;
+  const FpMapKey key{p->v.fp_v, bstride, g.fp_capacity, g.num_kv_heads, g.batch};
+  std::lock_guard<std::mutex> lock(g_map_mutex);
+  for (const FpMapEntry& e : g_maps)
+    if (e.used && e.key == key) { p->fp_map = e.map; p->fp_tma = 1; return; }
+  const cuuint64_t dims[4] = {128, (cuuint64_t)g.fp_capacity, (cuuint64_t)g.num_kv_heads, (cuuint64_t)g.batch};
+  const cuuint64_t strides[3] = {256, (cuuint64_t)g.fp_capacity * 256, (cuuint64_t)bstride};
+  const cuuint32_t box[4] = {64, (cuuint32_t)kTF, 1, 1};
+  const cuuint32_t estr[4] = {1, 1, 1, 1};
+  CUtensorMap map;
+  if (encode(&map, CU_TENSOR_MAP_DATA_TYPE_UINT16, 4, const_cast<void*>(p->v.fp_v), dims, strides, box, estr,
+             CU_TENSOR_MAP_INTERLEAVE_NONE, CU_TENSOR_MAP_SWIZZLE_128B, CU_TENSOR_MAP_L2_PROMOTION_L2_128B,
+             CU_TENSOR_MAP_FLOAT_OOB_FILL_NONE) != CUDA_SUCCESS)
+    return;
+  FpMapEntry& slot = g_maps[g_map_next];
+  g_map_next = (g_map_next + 1) % 8;
+  slot.key = key; slot.map = map; slot.used = true;
+  p->fp_map = map;
+  p->fp_tma = 1;
 }
 
 template <bool BF16>
@@ -257,6 +316,7 @@ int r2k_decode(const R2KGeom* geom, const R2KCacheView* view, const void* q, con
   p.group_counter = p.req_counter + p.g.batch;
   p.partials = reinterpret_cast<float*>(ws + kWsHeaderBytes + counters_bytes(p));
   p.group_partials = p.partials + (size_t)p.bh_total * p.parts_cap * kSlotFloats;
+  bind_fp_map(&p);
 
   DeviceInfo* dev;
   rc = device_info(&dev);
