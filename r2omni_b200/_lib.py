@@ -53,6 +53,10 @@ def lib():
         handle.r2k_launch_count.restype = C.c_uint64
         for name in EXPORTS[2:]:
             getattr(handle, name).restype = C.c_int
+        # the per-step call: declared argument types let plain ints and byref() objects through without
+        # building a ctypes wrapper per argument
+        handle.r2k_decode.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p,
+                                      C.c_uint32, C.c_void_p]
         _lib = handle
     return _lib
 

@@ -114,6 +114,13 @@ class SplitKExecutor:
         self._lib = L.lib()
         self._geom = arenas.geom(self.num_query_heads, sm_scale=self.sm_scale)
         self._idx = None
+        # per-step constants of the launch, built once
+        self._decode = self._lib.r2k_decode
+        self._geom_ref = C.byref(self._geom)
+        self._append_ref = C.byref(self._append)
+        self._view_obj, self._view_ref = None, None
+        self._ws_ptr, self._ws_size = workspace.buffer.data_ptr(), workspace.buffer.numel()
+        self._qshape = (arenas.batch, self.num_query_heads, 128)
 
     @property
     def batched(self) -> bool:
@@ -123,18 +130,20 @@ class SplitKExecutor:
         a = self.arenas
         geom = self._geom
         geom.n_i2 = a.i2_active   # the only extent that moves during generation (flushes)
-        ws = self.workspace.buffer
-        L.check(self._lib.r2k_decode(
-            C.byref(geom), C.byref(a.view()), C.c_void_p(query.data_ptr()), append,
-            C.c_void_p(ws.data_ptr()), C.c_size_t(ws.numel()), C.c_void_p(out_ptr), C.c_uint32(flags),
-            C.c_void_p(_stream_ptr(a.device))), "r2k_decode")
+        view = a.view()
+        if view is not self._view_obj:
+            self._view_obj, self._view_ref = view, C.byref(view)
+        status = self._decode(self._geom_ref, self._view_ref, query.data_ptr(), append, self._ws_ptr, self._ws_size, out_ptr,
+                              flags, _stream_ptr(a.device))
+        if status:
+            L.check(status, "r2k_decode")
 
     def _check_query(self, query: torch.Tensor) -> torch.Tensor:
         if query.ndim == 4:
             query = query[:, :, 0]
         a = self.arenas
-        if (tuple(query.shape) != (a.batch, self.num_query_heads, 128) or query.device != a.device
-                or not query.is_contiguous() or query.dtype != a.dtype):
+        if (query.shape != self._qshape or query.device != a.device or not query.is_contiguous()
+                or query.dtype != a.dtype):
             raise ValueError("query does not match prepared split-K executor")
         return query
 
@@ -165,7 +174,7 @@ class SplitKExecutor:
                 cols.append(t)
             self._idx = torch.stack(cols, dim=1).contiguous()
             ap.indices, ap.global_index, ap.logical_position = self._idx.data_ptr(), 0, 0
-        return C.byref(ap)
+        return self._append_ref
 
     def __call__(self, query: torch.Tensor, append=None) -> torch.Tensor:
         query = self._check_query(query)
