@@ -272,8 +272,9 @@ def time_region(device, fn, dist_on):
 
 def sharded_1m(device, rank, world, steps, warmup, dist_on):
     """Sequence-sharded decode of a 1,048,576-token cache (INT4/INT2 value pages 50/50,
-    128-token residual window on the last rank): per-rank un-normalised state, one
-    all-gather over NCCL, merge on every rank."""
+    128-token residual window on the last rank).  With more than one rank the merge is fused into the decode
+    launch (peer stores over NVLink, r2k_decode_exchange); the all-gather + merge-launch variant is timed
+    beside it for comparison."""
     import torch.distributed as dist
 
     import r2omni_b200 as R
@@ -298,42 +299,51 @@ def sharded_1m(device, rank, world, steps, warmup, dist_on):
                                      logical_position=total + i, stats=st)
     a = cache.arenas
     my_bytes = algorithmic_bytes(a.n_fp, a.n_i4, a.i2_active, a.recent_len, 1, append=False)
-    sharded = R.SequenceShardedExecutor(ex) if world > 1 else None
-
-    def one_step():
-        if world == 1:
-            ex(q)
+    def timed(one_step, steps):
+        """(us per step, graphed?) for `steps` steps; eight steps per CUDA graph, eager launches if capture is refused."""
+        for _ in range(max(warmup, 3)):
+            one_step()
+        torch.cuda.synchronize(device)
+        graph, per_replay = None, 8
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                for _ in range(per_replay):
+                    one_step()
+            graph.replay()
+            torch.cuda.synchronize(device)
+        except Exception:
+            graph = None
+            torch.cuda.synchronize(device)
+        if graph is not None:
+            steps = max(per_replay, steps // per_replay * per_replay)
+            ms, _ = time_region(device, lambda: [graph.replay() for _ in range(steps // per_replay)], dist_on)
         else:
-            sharded(q)
+            ms, _ = time_region(device, lambda: [one_step() for _ in range(steps)], dist_on)
+        return ms * 1e3 / steps, graph is not None, steps
 
-    for _ in range(max(warmup, 3)):
-        one_step()
-    # eight steps per CUDA graph (the all-gather is captured too); eager launches if capture is refused
-    torch.cuda.synchronize(device)
-    graph, per_replay = None, 8
-    try:
-        graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(graph):
-            for _ in range(per_replay):
-                one_step()
-        graph.replay()
-        torch.cuda.synchronize(device)
-    except Exception:
-        graph = None
-        torch.cuda.synchronize(device)
-    if graph is not None:
-        steps = max(per_replay, steps // per_replay * per_replay)
-        ms, _ = time_region(device, lambda: [graph.replay() for _ in range(steps // per_replay)], dist_on)
+    nccl_us = None
+    if world == 1:
+        us, graphed, steps = timed(lambda: ex(q), steps)
     else:
-        ms, _ = time_region(device, lambda: [one_step() for _ in range(steps)], dist_on)
+        gathered = R.SequenceShardedExecutor(ex)
+        nccl_us, _, _ = timed(lambda: gathered(q), steps)
+        fused = R.SequenceShardedExecutor(ex, fused=True, device_step_counter=True)
+        us, graphed, steps = timed(lambda: fused(q), steps)
+        status = ex.device_status()
+        fused.close()
+        if status != 0:
+            raise RuntimeError("the fused cross-rank merge reported a device-side timeout")
     bytes_all = torch.tensor([float(my_bytes)], device=device, dtype=torch.float64)
     if dist_on:
         dist.all_reduce(bytes_all)
-    us = ms * 1e3 / steps
-    return {"workload": "sharded_1m_b1", "tokens": total, "n_gpus": world, "us_per_step": round(us, 2),
-            "gbps": round(float(bytes_all.item()) / (us * 1e-6) / 1e9, 1), "steps": steps,
-            "collective": "none" if world == 1 else "nccl all_gather of [Hq,130] fp32 per rank",
-            "launches_per_step": 1 if world == 1 else 2, "cuda_graph": graph is not None}
+    out = {"workload": "sharded_1m_b1", "tokens": total, "n_gpus": world, "us_per_step": round(us, 2),
+           "gbps": round(float(bytes_all.item()) / (us * 1e-6) / 1e9, 1), "steps": steps,
+           "collective": "none" if world == 1 else "fused: peer stores + flags inside the decode launch",
+           "launches_per_step": 1, "cuda_graph": graphed}
+    if nccl_us is not None:
+        out["us_per_step_nccl_all_gather"] = round(nccl_us, 2)
+    return out
 
 
 def cpu_baseline_sample(tokens, seconds=12.0):

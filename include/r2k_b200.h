@@ -190,6 +190,51 @@ uint64_t r2k_launch_count(void);
 int r2k_merge_states(const float* states, int32_t num_states, int64_t state_stride, int32_t rows,
                      int32_t dtype, void* out, uint32_t flags, void* stream);
 
+/* ---- sequence-sharded decode with the merge fused over peer memory -------- */
+
+/*
+ * One exchange buffer per rank (GPU), mapped into every rank's address space.
+ * A decode launched through r2k_decode_exchange ends, for every (request, kv
+ * head), by storing this rank's un-normalised state rows into EVERY rank's
+ * buffer over NVLink (plain peer stores), publishing a step flag, waiting
+ * (bounded) for the other ranks' flags in its own buffer and merging all
+ * ranks' rows there -- the exact merge of r2k_merge_states.  Every rank ends
+ * with the same output; there is no collective launch and no merge launch.
+ * No counterpart in the reference (it has no multi-GPU path); the arithmetic
+ * is _merge_state, r2omni/sspa/kernels/triton_fourq_attention.py:58-69.
+ *
+ * Rules: world <= R2K_MAX_RANKS, one process per GPU, every rank makes the
+ * call for every step with the same `seq` (1, 2, 3, ...; or 0 on every rank and
+ * every step: the kernel then counts the steps itself in the exchange buffer,
+ * which is what a captured CUDA graph needs; two steps in flight
+ * never share a buffer half because a rank cannot finish step n+1 before every
+ * rank has finished step n).  A rank that is missing makes the others give up
+ * after a bounded wait (about a second) and report R2K_ERR_DEVICE_TIMEOUT through
+ * r2k_decode_device_status; nothing hangs.
+ */
+#define R2K_MAX_RANKS 8
+typedef struct R2KExchange {
+  void*    buffers[R2K_MAX_RANKS]; /* rank r's exchange buffer as mapped in this process */
+  int32_t  rank, world;
+  uint32_t seq;                    /* step counter 1, 2, 3, ... or 0: use the counter kept in the buffer */
+  uint32_t reserved;
+} R2KExchange;
+
+/* Bytes of one rank's exchange buffer for this geometry and world size. */
+int r2k_exchange_bytes(const R2KGeom* geom, int32_t world, size_t* bytes);
+/* Set-up only (these three allocate / map device memory; nothing else in this
+ * library does): a zeroed device buffer plus its 64-byte inter-process handle;
+ * a mapping of another rank's buffer (peer access is enabled on the way); and
+ * their release (`opened` != 0 for a mapping obtained from r2k_exchange_open). */
+int r2k_exchange_create(size_t bytes, void** buffer, unsigned char handle[64]);
+int r2k_exchange_open(const unsigned char handle[64], void** buffer);
+int r2k_exchange_close(void* buffer, int32_t opened);
+/* r2k_decode plus the fused cross-rank merge described above.  `out` receives
+ * the merged, normalised output; R2K_FLAG_OUT_STATE is not accepted. */
+int r2k_decode_exchange(const R2KGeom* geom, const R2KCacheView* view, const void* q, const R2KAppend* append,
+                        void* workspace, size_t workspace_bytes, void* out, uint32_t flags,
+                        const R2KExchange* exchange, void* stream);
+
 /* ---- quantize and pack -------------------------------------------------- */
 
 /*

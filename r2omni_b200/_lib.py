@@ -14,6 +14,7 @@ EXPORTS = (
     "r2k_status_string", "r2k_launch_count", "r2k_decode_workspace_bytes", "r2k_decode_workspace_init", "r2k_decode",
     "r2k_decode_static", "r2k_decode_device_status", "r2k_merge_states", "r2k_pack_k_int4", "r2k_pack_v_int4", "r2k_pack_v_int2",
     "r2k_gather_rows", "r2k_fwht128", "r2k_append_recent", "r2k_flush_recent",
+    "r2k_exchange_bytes", "r2k_exchange_create", "r2k_exchange_open", "r2k_exchange_close", "r2k_decode_exchange",
 )
 
 
@@ -37,6 +38,15 @@ class Append(C.Structure):
                 ("global_index", C.c_int64), ("logical_position", C.c_int64)]
 
 
+MAX_RANKS = 8
+
+
+class Exchange(C.Structure):
+    """include/r2k_b200.h: R2KExchange."""
+    _fields_ = [("buffers", C.c_void_p * MAX_RANKS), ("rank", C.c_int32), ("world", C.c_int32), ("seq", C.c_uint32),
+                ("reserved", C.c_uint32)]
+
+
 _lib = None
 
 
@@ -57,6 +67,7 @@ def lib():
         # building a ctypes wrapper per argument
         handle.r2k_decode.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p,
                                       C.c_uint32, C.c_void_p]
+        handle.r2k_decode_exchange.argtypes = handle.r2k_decode.argtypes[:8] + [C.c_void_p, C.c_void_p]
         _lib = handle
     return _lib
 

@@ -271,8 +271,13 @@ int r2k_decode_workspace_init(void* workspace, size_t bytes, void* stream) {
   return cudaMemsetAsync(workspace, 0, n, reinterpret_cast<cudaStream_t>(stream)) == cudaSuccess ? R2K_OK : R2K_ERR_CUDA;
 }
 
-int r2k_decode(const R2KGeom* geom, const R2KCacheView* view, const void* q, const R2KAppend* append, void* workspace,
-               size_t workspace_bytes, void* out, uint32_t flags, void* stream) {
+static size_t exchange_states_bytes(const R2KGeom* g, int world) {
+  const size_t n = (size_t)2 * world * g->batch * g->num_q_heads * 130 * sizeof(float);
+  return (n + 127) / 128 * 128;
+}
+
+static int decode_impl(const R2KGeom* geom, const R2KCacheView* view, const void* q, const R2KAppend* append, void* workspace,
+                       size_t workspace_bytes, void* out, uint32_t flags, const R2KExchange* ex, void* stream) {
   if (view == nullptr || q == nullptr || workspace == nullptr || out == nullptr) return R2K_ERR_NULL;
   int rc = check_geom(geom);
   if (rc) return rc;
@@ -317,6 +322,16 @@ int r2k_decode(const R2KGeom* geom, const R2KCacheView* view, const void* q, con
   p.partials = reinterpret_cast<float*>(ws + kWsHeaderBytes + counters_bytes(p));
   p.group_partials = p.partials + (size_t)p.bh_total * p.parts_cap * kSlotFloats;
   bind_fp_map(&p);
+  if (ex != nullptr && ex->world > 1) {
+    if (ex->world > R2K_MAX_RANKS || ex->rank < 0 || ex->rank >= ex->world || (flags & R2K_FLAG_OUT_STATE)) return R2K_ERR_GEOMETRY;
+    for (int r = 0; r < ex->world; ++r) {
+      if (ex->buffers[r] == nullptr) return R2K_ERR_NULL;
+      if (!aligned16(ex->buffers[r])) return R2K_ERR_ALIGNMENT;
+      p.xbuf[r] = reinterpret_cast<float*>(ex->buffers[r]);
+    }
+    p.xw = ex->world; p.xrank = ex->rank; p.xseq = ex->seq;
+    p.xflags_off = (uint32_t)exchange_states_bytes(geom, ex->world);
+  }
 
   DeviceInfo* dev;
   rc = device_info(&dev);
@@ -347,6 +362,60 @@ int r2k_decode(const R2KGeom* geom, const R2KCacheView* view, const void* q, con
                                                         : cudaLaunchKernelEx(&cfg, decode_kernel<false>, p);
   ++g_launches;
   return err == cudaSuccess ? R2K_OK : R2K_ERR_CUDA;
+}
+
+int r2k_decode(const R2KGeom* geom, const R2KCacheView* view, const void* q, const R2KAppend* append, void* workspace,
+               size_t workspace_bytes, void* out, uint32_t flags, void* stream) {
+  return decode_impl(geom, view, q, append, workspace, workspace_bytes, out, flags, nullptr, stream);
+}
+
+int r2k_decode_exchange(const R2KGeom* geom, const R2KCacheView* view, const void* q, const R2KAppend* append, void* workspace,
+                        size_t workspace_bytes, void* out, uint32_t flags, const R2KExchange* exchange, void* stream) {
+  if (exchange == nullptr) return R2K_ERR_NULL;
+  if (exchange->world < 1) return R2K_ERR_GEOMETRY;
+  return decode_impl(geom, view, q, append, workspace, workspace_bytes, out, flags, exchange, stream);
+}
+
+int r2k_exchange_bytes(const R2KGeom* geom, int32_t world, size_t* bytes) {
+  if (bytes == nullptr) return R2K_ERR_NULL;
+  int rc = check_geom(geom);
+  if (rc) return rc;
+  if (world < 1 || world > R2K_MAX_RANKS) return R2K_ERR_GEOMETRY;
+  const size_t flags = (size_t)2 * world * geom->batch * geom->num_kv_heads * sizeof(uint32_t);
+  *bytes = exchange_states_bytes(geom, world) + (flags + 127) / 128 * 128 + 128;   // + device step counter
+  return R2K_OK;
+}
+
+int r2k_exchange_create(size_t bytes, void** buffer, unsigned char handle[64]) {
+  if (buffer == nullptr || handle == nullptr) return R2K_ERR_NULL;
+  static_assert(sizeof(cudaIpcMemHandle_t) == 64, "inter-process handle size");
+  if (bytes == 0) return R2K_ERR_GEOMETRY;
+  void* ptr = nullptr;
+  if (cudaMalloc(&ptr, bytes) != cudaSuccess) return R2K_ERR_CUDA;
+  cudaIpcMemHandle_t h;
+  if (cudaMemset(ptr, 0, bytes) != cudaSuccess || cudaIpcGetMemHandle(&h, ptr) != cudaSuccess) {
+    cudaFree(ptr);
+    return R2K_ERR_CUDA;
+  }
+  std::memcpy(handle, &h, 64);
+  *buffer = ptr;
+  return R2K_OK;
+}
+
+int r2k_exchange_open(const unsigned char handle[64], void** buffer) {
+  if (buffer == nullptr || handle == nullptr) return R2K_ERR_NULL;
+  cudaIpcMemHandle_t h;
+  std::memcpy(&h, handle, 64);
+  void* ptr = nullptr;
+  if (cudaIpcOpenMemHandle(&ptr, h, cudaIpcMemLazyEnablePeerAccess) != cudaSuccess) return R2K_ERR_CUDA;
+  *buffer = ptr;
+  return R2K_OK;
+}
+
+int r2k_exchange_close(void* buffer, int32_t opened) {
+  if (buffer == nullptr) return R2K_OK;
+  const cudaError_t e = opened ? cudaIpcCloseMemHandle(buffer) : cudaFree(buffer);
+  return e == cudaSuccess ? R2K_OK : R2K_ERR_CUDA;
 }
 
 }  // extern "C"

@@ -218,6 +218,25 @@ class SplitKExecutor:
             self.arenas.recent_len += 1
         return out
 
+    def decode_exchange(self, query: torch.Tensor, exchange, out: torch.Tensor, append=None) -> torch.Tensor:
+        """Sequence-sharded step with the cross-rank merge fused into the launch (``r2k_decode_exchange``):
+        ``exchange`` is the rank's ``R2KExchange`` with this step's counter, ``out`` receives the merged output."""
+        query = self._check_query(query)
+        a = self.arenas
+        if a.dtype != torch.bfloat16 or out.dtype != torch.bfloat16:
+            raise ValueError("the fused sharded step writes bf16 output for a bf16 cache")
+        ap = self._make_append(append, query)
+        self._geom.n_i2 = a.i2_active
+        view = a.view()
+        flags = L.FLAG_OUTPUT_HADAMARD if self.output_hadamard else 0
+        status = self._lib.r2k_decode_exchange(C.byref(self._geom), C.byref(view), query.data_ptr(), ap, self._ws_ptr,
+                                               self._ws_size, out.data_ptr(), flags, C.byref(exchange), _stream_ptr(a.device))
+        if status:
+            L.check(status, "r2k_decode_exchange")
+        if append is not None and self.batched:
+            a.recent_len += 1
+        return out
+
     def device_status(self) -> int:
         status = C.c_int32(0)
         L.check(self._lib.r2k_decode_device_status(C.c_void_p(self.workspace.buffer.data_ptr()), C.byref(status),

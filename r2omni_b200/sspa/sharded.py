@@ -9,6 +9,11 @@ state per query head, and the states are combined with ONE all-gather of
 ``B*Hq*130`` floats followed by the exact merge of
 r2omni/sspa/kernels/triton_fourq_attention.py:58-69 on every rank.  The residual
 window and the flush live on the last rank only.
+
+``fused=True`` replaces the all-gather and the merge launch by peer stores inside
+the decode kernel: every rank's last CTA of a (request, kv head) writes its state
+rows into every rank's exchange buffer over NVLink, raises a step flag, waits
+(bounded) for the others' flags and merges in place (``r2k_decode_exchange``).
 """
 from __future__ import annotations
 
@@ -46,12 +51,19 @@ class SequenceShardedExecutor:
     make the same call.
     """
 
-    def __init__(self, local: SplitKExecutor, group=None):
+    def __init__(self, local: SplitKExecutor, group=None, *, fused: bool = False, device_step_counter: bool = False):
         import torch.distributed as dist
         self._dist = dist
         self.local, self.group = local, group
         self.world = dist.get_world_size(group) if dist.is_initialized() else 1
         self.rank = dist.get_rank(group) if dist.is_initialized() else 0
+        self.fused = bool(fused) and self.world > 1
+        # the step counter of the fused merge lives on the host (one integer per call) or, for calls that are
+        # captured into a CUDA graph and replayed, on the device
+        self.device_step_counter = bool(device_step_counter)
+        self._exchange, self._mapped, self._own = None, [], None
+        if self.fused:
+            self._open_exchange()
         a = local.arenas
         shape = (a.batch, local.num_query_heads, 130)
         self.state = torch.empty(shape, device=a.device, dtype=torch.float32)
@@ -60,10 +72,53 @@ class SequenceShardedExecutor:
         self._staging = None if a.dtype == torch.bfloat16 else torch.empty(self.output.shape, device=a.device,
                                                                            dtype=torch.float32)
 
+    def _open_exchange(self) -> None:
+        """One exchange buffer per rank, created here and mapped into every other rank through its 64-byte
+        inter-process handle (exchanged with one all_gather_object)."""
+        if self.world > L.MAX_RANKS:
+            raise ValueError(f"the fused merge supports at most {L.MAX_RANKS} ranks")
+        lib, a = L.lib(), self.local.arenas
+        geom = a.geom(self.local.num_query_heads)
+        need = C.c_size_t(0)
+        L.check(lib.r2k_exchange_bytes(C.byref(geom), self.world, C.byref(need)), "r2k_exchange_bytes")
+        own, handle = C.c_void_p(0), (C.c_ubyte * 64)()
+        with torch.cuda.device(a.device):
+            L.check(lib.r2k_exchange_create(C.c_size_t(need.value), C.byref(own), handle), "r2k_exchange_create")
+            handles = [None] * self.world
+            self._dist.all_gather_object(handles, (self.rank, bytes(handle)), group=self.group)
+            ex = L.Exchange()
+            ex.rank, ex.world, ex.seq = self.rank, self.world, 0
+            for r, raw in handles:
+                if r == self.rank:
+                    ex.buffers[r] = own.value
+                    continue
+                ptr = C.c_void_p(0)
+                L.check(lib.r2k_exchange_open((C.c_ubyte * 64).from_buffer_copy(raw), C.byref(ptr)), "r2k_exchange_open")
+                ex.buffers[r] = ptr.value
+                self._mapped.append(ptr.value)
+        self._own, self._exchange = own.value, ex
+        self._dist.barrier(group=self.group)   # nobody starts a step before every mapping exists
+
+    def close(self) -> None:
+        """Unmap the peers' buffers and free this rank's (call on every rank, after the last step completed)."""
+        if self._exchange is None:
+            return
+        torch.cuda.synchronize(self.local.arenas.device)
+        self._dist.barrier(group=self.group)
+        lib = L.lib()
+        for ptr in self._mapped:
+            lib.r2k_exchange_close(C.c_void_p(ptr), 1)
+        self._dist.barrier(group=self.group)
+        lib.r2k_exchange_close(C.c_void_p(self._own), 0)
+        self._exchange, self._mapped, self._own, self.fused = None, [], None, False
+
     def __call__(self, query: torch.Tensor, append=None) -> torch.Tensor:
         ex = self.local
         a = ex.arenas
         mine = append if self.rank == self.world - 1 else None
+        if self.fused:
+            self._exchange.seq = 0 if self.device_step_counter else ((self._exchange.seq + 1) & 0xFFFFFFFF or 1)
+            return ex.decode_exchange(query, self._exchange, self.output, append=mine)
         ex.decode_state(query, out=self.state, append=mine)
         if self.world > 1:
             self._dist.all_gather_into_tensor(self.gathered, self.state, group=self.group)

@@ -39,14 +39,15 @@ def test_library_exports_every_declared_symbol(lib):
 
 def test_struct_layouts_match_the_header(tmp_path):
     src = tmp_path / "sizes.c"
-    src.write_text('#include <stdio.h>\n#include <stddef.h>\n#include "r2k_b200.h"\nint main(void){printf("%zu %zu %zu %zu %zu %zu\\n",'
+    src.write_text('#include <stdio.h>\n#include <stddef.h>\n#include "r2k_b200.h"\nint main(void){printf("%zu %zu %zu %zu %zu %zu %zu %zu\\n",'
                    "sizeof(R2KGeom), sizeof(R2KCacheView), sizeof(R2KAppend), offsetof(R2KGeom, sm_scale),"
-                   "offsetof(R2KCacheView, k_packed_bstride), offsetof(R2KAppend, global_index));return 0;}\n")
+                   "offsetof(R2KCacheView, k_packed_bstride), offsetof(R2KAppend, global_index),"
+                   "sizeof(R2KExchange), offsetof(R2KExchange, seq));return 0;}\n")
     exe = tmp_path / "sizes"
     subprocess.run(["gcc", "-I", os.path.join(ROOT, "include"), "-o", str(exe), str(src)], check=True)
     got = [int(x) for x in subprocess.run([str(exe)], capture_output=True, text=True, check=True).stdout.split()]
     want = [C.sizeof(L.Geom), C.sizeof(L.CacheView), C.sizeof(L.Append), L.Geom.sm_scale.offset,
-            L.CacheView.k_packed_bstride.offset, L.Append.global_index.offset]
+            L.CacheView.k_packed_bstride.offset, L.Append.global_index.offset, C.sizeof(L.Exchange), L.Exchange.seq.offset]
     assert got == want
 
 
