@@ -509,6 +509,16 @@ def main():
                 "bytes_per_launch": int(k_bytes / max(probe_steps, 1)),
                 "traffic": NCU_DRAM_BYTES_PER_LAUNCH if args.workload == "decode_32k_b8" and args.page_mix == "25,50,25" else None}
 
+    # the flush alone (quantize-and-pack of the 128-token residual window: 3 launches, launch-bound)
+    def flush_only():
+        for r in range(8):
+            for s_, e in enumerate(bench.ex):
+                bench.flush_graphs[s_].replay()
+                e.arenas.recent_len = 0
+    f_ms, _ = time_region(device, flush_only, dist_on)
+    flush = {"us_per_flush": round(f_ms * 1e3 / (8 * len(bench.ex)), 2), "launches": bench.launches_per_flush,
+             "amortised_us_per_step": round(f_ms * 1e3 / (8 * len(bench.ex)) / RING, 3)}
+
     # end to end through the operator call with host buffers
     e2e = None
     if not args.no_e2e:
@@ -540,7 +550,7 @@ def main():
                        "l2": "4 cache sets of ~98 MB visited round-robin (inputs larger than L2)",
                        "parallelism": f"{world} independent replicas" if world > 1 else "1 GPU",
                        "step_bytes": bench_bytes_note(tokens, batch)},
-            "gpu_launches": int(gpu_launches), "flushes_in_region": int(flushes),
+            "gpu_launches": int(gpu_launches), "flushes_in_region": int(flushes), "flush": flush,
             "roofline": roofline, "e2e": e2e, "clocks": clocks.summary(),
         }
         if cpu is not None:
