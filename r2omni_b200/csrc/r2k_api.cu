@@ -83,7 +83,7 @@ int derive(const R2KGeom* g, DecodeParams* p) {
   // are measured per-tile times (ns of one CTA slot on B200, pure-pool caches), scaled down until a whole
   // (request, kv head) fits in 22 bits: the kernel's partition arithmetic is 32-bit.
   (void)g2;
-  const double ns[4] = {1290.0, 2110.0, 2310.0, 450.0};
+  const double ns[4] = {1400.0, 2110.0, 2400.0, 450.0};
   const int64_t cnt[4] = {p->nF, p->n4, p->n2, p->nR};
   double scale = 100.0;
   uint32_t w[4];
