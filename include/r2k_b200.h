@@ -283,6 +283,18 @@ int r2k_gather_rows(const void* src, int32_t num_kv_heads, int64_t src_rows, con
  * the pre-conditioning of new key/value rows when key_hadamard / value_hadamard is on. */
 int r2k_fwht128(const void* in, void* out, int32_t dtype, int64_t rows, void* stream);
 
+/* Qwen multimodal rotary embedding of q [B,Hq,T,128] and k [B,Hkv,T,128] (contiguous, 16-bit type `dtype`) in
+ * one launch, optionally followed by the 128-point Hadamard transform of every row.  cos / sin are addressed as
+ * [axis(3), request, token, channel] with the given element strides; rot_dtype is R2K_DTYPE_BF16, R2K_DTYPE_FP16
+ * or 2 for float32; axis(d) is 0 for (d mod 64) < section0, 1 below section0 + section1, else 2.  Outputs may
+ * alias the inputs.  Replaces qwen_qk_mrope / _qwen_qk_mrope_kernel / _qwen_batched_qk_mrope_kernel
+ * (r2omni/sspa/kernels/triton_qwen_mrope.py:44-124, 126-212, 214-322), the prologue that produces the query and
+ * the new key row of a decode step (r2omni/sspa/integration/qwen_sspa_attention.py:1239-1247). */
+int r2k_qk_mrope(const void* q, const void* k, void* q_out, void* k_out, int32_t dtype, int32_t batch,
+                 int32_t num_q_heads, int32_t num_kv_heads, int32_t tokens, const void* cos, const void* sin,
+                 int32_t rot_dtype, const int64_t cos_strides[4], const int64_t sin_strides[4], int32_t section0,
+                 int32_t section1, int32_t apply_hadamard, void* stream);
+
 /* ---- residual window ---------------------------------------------------- */
 
 /*

@@ -140,6 +140,29 @@ def fwht128(x: torch.Tensor) -> torch.Tensor:
     return out * n ** -0.5
 
 
+def qk_mrope(query: torch.Tensor, key: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, sections,
+             apply_hadamard: bool = False):
+    """Qwen multimodal RoPE of q [B,Hq,T,128] and k [B,Hkv,T,128] with cos / sin [3,B,T,128], then optionally the
+    Hadamard transform; elementwise restatement of _qwen_qk_mrope_kernel
+    (r2omni/sspa/kernels/triton_qwen_mrope.py:44-124): out[d] = x[d]*cos[axis(d)] + rot(x)[d]*sin[axis(d)],
+    rot(x)[d] = -x[d+64] for d < 64 and x[d-64] above, axis by the section of d mod 64, fp32, rounded to the
+    input type.  Parity unpinned: the reference has no CPU form of this kernel to run against."""
+    d = torch.arange(128)
+    sd = d % 64
+    axis = torch.where(sd < sections[0], 0, torch.where(sd < sections[0] + sections[1], 1, 2))
+    c = cos.float()[axis, :, :, d].permute(1, 2, 0)      # [B,T,128]
+    s = sin.float()[axis, :, :, d].permute(1, 2, 0)
+    outs = []
+    for x in (query, key):
+        xf = x.float()
+        rot = torch.cat((-xf[..., 64:], xf[..., :64]), dim=-1)
+        y = xf * c[:, None] + rot * s[:, None]
+        if apply_hadamard:
+            y = fwht128(y)
+        outs.append(y.to(x.dtype))
+    return outs[0], outs[1]
+
+
 # --------------------------------------------------------------------------- #
 # cache
 # --------------------------------------------------------------------------- #

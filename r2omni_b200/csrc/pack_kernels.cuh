@@ -289,4 +289,84 @@ __global__ void fwht128_kernel(const uint16_t* __restrict__ in, uint16_t* __rest
   *reinterpret_cast<uint2*>(out + row * 128 + 4 * lane) = pk;
 }
 
+// ---------------------------------------------------------------------------
+// Qwen multimodal rotary embedding of the query and key rows of a step, optionally followed by the 128-point
+// Hadamard transform, in one launch: row (request, head, token) of q or k, out[d] = x[d] * cos[axis(d)] +
+// rot(x)[d] * sin[axis(d)] with rot(x)[d] = -x[d + 64] (d < 64), x[d - 64] (d >= 64) and axis(d) chosen by the
+// section of d mod 64.  fp32 arithmetic, products and sum rounded separately (as the elementwise CPU form),
+// result rounded to the element type.  One warp per row, four consecutive channels per lane.
+// ---------------------------------------------------------------------------
+struct MropeArgs {
+  const uint16_t* q; const uint16_t* k; uint16_t* q_out; uint16_t* k_out;
+  const void* cos; const void* sin;
+  int64_t cos_stride[4], sin_stride[4];   // elements: axis, request, token, channel
+  int batch, hq, hkv, tokens, section0, section1, rot_dtype, hadamard;   // rot_dtype: R2K_DTYPE_* or 2 for float32
+};
+
+__device__ __forceinline__ float load_rot(const void* base, int64_t index, int dtype) {
+  if (dtype == 2) return reinterpret_cast<const float*>(base)[index];
+  const uint16_t raw = reinterpret_cast<const uint16_t*>(base)[index];
+  return dtype == R2K_DTYPE_BF16 ? __uint_as_float((uint32_t)raw << 16) : __half2float(__ushort_as_half(raw));
+}
+
+template <bool BF16>
+__global__ void mrope_rows_kernel(MropeArgs a) {
+  const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
+  const int lane = threadIdx.x & 31;
+  const int heads = a.hq + a.hkv;
+  if (row >= (int64_t)a.batch * heads * a.tokens) return;
+  const int request = (int)(row / ((int64_t)heads * a.tokens));
+  const int local = (int)(row - (int64_t)request * heads * a.tokens);
+  const int head = local / a.tokens, token = local - head * a.tokens;
+  const bool is_q = head < a.hq;
+  const int64_t off = is_q ? (((int64_t)request * a.hq + head) * a.tokens + token) * 128
+                           : (((int64_t)request * a.hkv + (head - a.hq)) * a.tokens + token) * 128;
+  const uint2 raw = *reinterpret_cast<const uint2*>((is_q ? a.q : a.k) + off + 4 * lane);
+  float x[4];
+  if (BF16) {
+    x[0] = __uint_as_float(raw.x << 16); x[1] = __uint_as_float(raw.x & 0xffff0000u);
+    x[2] = __uint_as_float(raw.y << 16); x[3] = __uint_as_float(raw.y & 0xffff0000u);
+  } else {
+    const float2 lo = __half22float2(*reinterpret_cast<const __half2*>(&raw.x));
+    const float2 hi = __half22float2(*reinterpret_cast<const __half2*>(&raw.y));
+    x[0] = lo.x; x[1] = lo.y; x[2] = hi.x; x[3] = hi.y;
+  }
+  float r[4];
+#pragma unroll
+  for (int e = 0; e < 4; ++e) {
+    const int d = 4 * lane + e, sd = d & 63;
+    const float other = __shfl_xor_sync(0xffffffffu, x[e], 16);   // channel d +- 64 lives 16 lanes away
+    const float rotated = lane < 16 ? -other : other;
+    const int axis = sd < a.section0 ? 0 : (sd < a.section0 + a.section1 ? 1 : 2);
+    const float c = load_rot(a.cos, axis * a.cos_stride[0] + request * a.cos_stride[1] + token * a.cos_stride[2] + d * a.cos_stride[3],
+                             a.rot_dtype);
+    const float s = load_rot(a.sin, axis * a.sin_stride[0] + request * a.sin_stride[1] + token * a.sin_stride[2] + d * a.sin_stride[3],
+                             a.rot_dtype);
+    r[e] = __fadd_rn(__fmul_rn(x[e], c), __fmul_rn(rotated, s));
+  }
+  if (a.hadamard) {
+    const float p = __fadd_rn(r[0], r[1]), m = __fsub_rn(r[0], r[1]), c = __fadd_rn(r[2], r[3]), d = __fsub_rn(r[2], r[3]);
+    r[0] = __fadd_rn(p, c); r[1] = __fadd_rn(m, d); r[2] = __fsub_rn(p, c); r[3] = __fsub_rn(m, d);
+#pragma unroll
+    for (int sft = 1; sft < 32; sft <<= 1) {
+#pragma unroll
+      for (int e = 0; e < 4; ++e) {
+        const float o = __shfl_xor_sync(0xffffffffu, r[e], sft);
+        r[e] = (lane & sft) ? __fsub_rn(o, r[e]) : __fadd_rn(r[e], o);
+      }
+    }
+#pragma unroll
+    for (int e = 0; e < 4; ++e) r[e] = __fmul_rn(r[e], 0.08838834764831845f);
+  }
+  uint2 pk;
+  if (BF16) {
+    __nv_bfloat162 lo = __floats2bfloat162_rn(r[0], r[1]), hi = __floats2bfloat162_rn(r[2], r[3]);
+    pk.x = *reinterpret_cast<uint32_t*>(&lo); pk.y = *reinterpret_cast<uint32_t*>(&hi);
+  } else {
+    __half2 lo = __floats2half2_rn(r[0], r[1]), hi = __floats2half2_rn(r[2], r[3]);
+    pk.x = *reinterpret_cast<uint32_t*>(&lo); pk.y = *reinterpret_cast<uint32_t*>(&hi);
+  }
+  *reinterpret_cast<uint2*>((is_q ? a.q_out : a.k_out) + off + 4 * lane) = pk;
+}
+
 }  // namespace r2k

@@ -554,6 +554,34 @@ int r2k_fwht128(const void* in, void* out, int32_t dtype, int64_t rows, void* st
   return cudaGetLastError() == cudaSuccess ? R2K_OK : R2K_ERR_CUDA;
 }
 
+int r2k_qk_mrope(const void* q, const void* k, void* q_out, void* k_out, int32_t dtype, int32_t batch, int32_t num_q_heads,
+                 int32_t num_kv_heads, int32_t tokens, const void* cos, const void* sin, int32_t rot_dtype,
+                 const int64_t cos_strides[4], const int64_t sin_strides[4], int32_t section0, int32_t section1,
+                 int32_t apply_hadamard, void* stream) {
+  if (!q || !k || !q_out || !k_out || !cos || !sin || !cos_strides || !sin_strides) return R2K_ERR_NULL;
+  if ((dtype != R2K_DTYPE_BF16 && dtype != R2K_DTYPE_FP16) || (rot_dtype != R2K_DTYPE_BF16 && rot_dtype != R2K_DTYPE_FP16 && rot_dtype != 2))
+    return R2K_ERR_GEOMETRY;
+  if (batch < 1 || num_q_heads < 1 || num_kv_heads < 1 || tokens < 1) return R2K_ERR_GEOMETRY;
+  if (section0 < 0 || section1 < 0 || section0 + section1 > 64) return R2K_ERR_GEOMETRY;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(q_out) |
+       reinterpret_cast<uintptr_t>(k_out)) & 7u)
+    return R2K_ERR_ALIGNMENT;
+  MropeArgs a;
+  a.q = reinterpret_cast<const uint16_t*>(q); a.k = reinterpret_cast<const uint16_t*>(k);
+  a.q_out = reinterpret_cast<uint16_t*>(q_out); a.k_out = reinterpret_cast<uint16_t*>(k_out);
+  a.cos = cos; a.sin = sin;
+  for (int i = 0; i < 4; ++i) { a.cos_stride[i] = cos_strides[i]; a.sin_stride[i] = sin_strides[i]; }
+  a.batch = batch; a.hq = num_q_heads; a.hkv = num_kv_heads; a.tokens = tokens;
+  a.section0 = section0; a.section1 = section1; a.rot_dtype = rot_dtype; a.hadamard = apply_hadamard ? 1 : 0;
+  const int64_t rows = (int64_t)batch * (num_q_heads + num_kv_heads) * tokens;
+  const unsigned grid = (unsigned)((rows + 3) / 4);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == R2K_DTYPE_BF16) mrope_rows_kernel<true><<<grid, 128, 0, st>>>(a);
+  else mrope_rows_kernel<false><<<grid, 128, 0, st>>>(a);
+  ++g_launches;
+  return cudaGetLastError() == cudaSuccess ? R2K_OK : R2K_ERR_CUDA;
+}
+
 int r2k_append_recent(const R2KGeom* geom, const R2KCacheView* view, const R2KAppend* append, void* stream) {
   if (view == nullptr || append == nullptr || append->k == nullptr || append->v == nullptr) return R2K_ERR_NULL;
   int rc = check_geom(geom);

@@ -1,0 +1,53 @@
+"""Qwen multimodal RoPE (+ Hadamard) prologue kernel against the oracle's elementwise restatement of
+_qwen_qk_mrope_kernel (r2omni/sspa/kernels/triton_qwen_mrope.py:44-124).  The kernel rounds the two products
+and their sum separately, as the elementwise form does, so the rounded result is bit-exact."""
+import pytest
+import torch
+
+import r2omni_b200 as R
+from oracle import sspa_oracle as O
+
+pytestmark = pytest.mark.gpu
+
+
+def _inputs(batch, hq, hkv, tokens, dtype, rot_dtype, seed):
+    g = torch.Generator().manual_seed(seed)
+    q = torch.randn(batch, hq, tokens, 128, generator=g).to(dtype)
+    k = torch.randn(batch, hkv, tokens, 128, generator=g).to(dtype)
+    angle = torch.rand(3, batch, tokens, 128, generator=g) * 6.2831853
+    return q, k, torch.cos(angle).to(rot_dtype), torch.sin(angle).to(rot_dtype)
+
+
+@pytest.mark.parametrize("dtype,rot_dtype", [(torch.bfloat16, torch.bfloat16), (torch.bfloat16, torch.float32),
+                                             (torch.float16, torch.float16)])
+@pytest.mark.parametrize("batch,hq,hkv,tokens", [(1, 16, 2, 1), (8, 16, 2, 1), (2, 28, 4, 3)])
+@pytest.mark.parametrize("hadamard", [False, True])
+def test_mrope_matches_the_oracle_bit_for_bit(dtype, rot_dtype, batch, hq, hkv, tokens, hadamard):
+    q, k, cos, sin = _inputs(batch, hq, hkv, tokens, dtype, rot_dtype, seed=batch * 100 + hq + tokens)
+    sections = (16, 24, 24)
+    want_q, want_k = O.qk_mrope(q, k, cos, sin, sections, hadamard)
+    got_q, got_k = R.qwen_qk_mrope(q.cuda(), k.cuda(), cos.cuda(), sin.cuda(), sections, apply_hadamard=hadamard)
+    assert torch.equal(got_q.cpu().view(torch.int16), want_q.view(torch.int16))
+    assert torch.equal(got_k.cpu().view(torch.int16), want_k.view(torch.int16))
+
+
+def test_mrope_strided_tables_in_place_output_and_errors():
+    q, k, cos, sin = _inputs(2, 16, 2, 1, torch.bfloat16, torch.float32, seed=9)
+    table = torch.zeros(3, 2, 5, 128)          # position tables are usually slices of longer ones
+    table_s = torch.zeros(3, 2, 5, 128)
+    table[:, :, 3:4] = cos
+    table_s[:, :, 3:4] = sin
+    want_q, want_k = O.qk_mrope(q, k, cos, sin, (16, 24, 24), True)
+    qd, kd = q.cuda(), k.cuda()
+    out = R.qwen_qk_mrope(qd, kd, table.cuda()[:, :, 3:4], table_s.cuda()[:, :, 3:4], (16, 24, 24), output=(qd, kd),
+                          apply_hadamard=True)
+    assert out[0] is qd and out[1] is kd
+    assert torch.equal(qd.cpu(), want_q) and torch.equal(kd.cpu(), want_k)
+    with pytest.raises(ValueError):
+        R.qwen_qk_mrope(qd, kd, cos.cuda(), sin.cuda(), (16, 24, 20))
+    with pytest.raises(ValueError):
+        R.qwen_qk_mrope(qd[0], kd, cos.cuda(), sin.cuda(), (16, 24, 24))
+    with pytest.raises(ValueError):
+        R.qwen_qk_mrope(qd, kd, cos.cuda()[:2], sin.cuda()[:2], (16, 24, 24))
+    with pytest.raises(RuntimeError):
+        R.qwen_qk_mrope(q, k, cos, sin, (16, 24, 24))
