@@ -177,7 +177,7 @@ __device__ __forceinline__ void qk_int4(uint32_t sb, const LaneOffsets& o, const
     float lo[4] = {0.f, 0.f, 0.f, 0.f}, hi[4] = {0.f, 0.f, 0.f, 0.f};
 #pragma unroll
     for (int i = 0; i < 4; ++i) {
-      const uint32_t a8 = __umulhi(wa[i], 1u << 24), b8 = __umulhi(wb[i], 1u << 24);   // >> 8 on the multiplier pipe
+      const uint32_t a8 = wa[i] >> 8, b8 = wb[i] >> 8;
       const uint32_t l0 = hsub2_u32(wa[i] & kMaskLo, zl[2 * i]), l1 = hsub2_u32(wb[i] & kMaskLo, zl[2 * i]);
       const uint32_t l2 = hsub2_u32(a8 & kMaskLo, zl[2 * i + 1]), l3 = hsub2_u32(b8 & kMaskLo, zl[2 * i + 1]);
       const uint32_t h0 = hsub2_u32(wa[i] & kMaskHi, zh[2 * i]), h1 = hsub2_u32(wb[i] & kMaskHi, zh[2 * i]);
@@ -218,7 +218,7 @@ __device__ __forceinline__ void pv_int4(WarpState& st, uint32_t sb, const LaneOf
     const uint32_t c0 = hf ? w0.y : w0.x, c1 = hf ? w1.y : w1.x, c2 = hf ? w2.y : w2.x, c3 = hf ? w3.y : w3.x;
     const uint32_t xa = __byte_perm(c0, c1, 0x5410), ya = __byte_perm(c0, c1, 0x7632);
     const uint32_t xb = __byte_perm(c2, c3, 0x5410), yb = __byte_perm(c2, c3, 0x7632);
-    const uint32_t xa8 = __umulhi(xa, 1u << 24), xb8 = __umulhi(xb, 1u << 24), ya8 = __umulhi(ya, 1u << 24), yb8 = __umulhi(yb, 1u << 24);
+    const uint32_t xa8 = xa >> 8, xb8 = xb >> 8, ya8 = ya >> 8, yb8 = yb >> 8;
     mma_f16(st.o[4 * hf + 0], (xa & kMaskLo) ^ kFixLo, (xa & kMaskHi) ^ kFixHi, (xb & kMaskLo) ^ kFixLo, (xb & kMaskHi) ^ kFixHi, b0, b1);
     mma_f16(st.o[4 * hf + 1], (xa8 & kMaskLo) ^ kFixLo, (xa8 & kMaskHi) ^ kFixHi, (xb8 & kMaskLo) ^ kFixLo, (xb8 & kMaskHi) ^ kFixHi, b0, b1);
     mma_f16(st.o[4 * hf + 2], (ya & kMaskLo) ^ kFixLo, (ya & kMaskHi) ^ kFixHi, (yb & kMaskLo) ^ kFixLo, (yb & kMaskHi) ^ kFixHi, b0, b1);
