@@ -221,27 +221,36 @@ __device__ __forceinline__ void produce_full_tile(const DecodeParams& p, const T
 }  // namespace
 
 // Exact merge of `count` partial rows (max, sum, out[128]) of head hh; this thread owns dims 8*sub .. 8*sub+7.
-// Loads are issued eight rows at a time so that their latencies overlap.
-__device__ __forceinline__ void merge_rows(const float* base, int count, int hh, int sub, float& mx, float& lsum,
-                                           float (&acc)[8]) {
+// Row `own` (or -1) is not loaded: the caller still holds it in registers (om, ol, oacc), which saves the merging
+// CTA a dependent round trip to memory for the common nine-partial head.  Rows are folded in slot order in
+// batches of nine slots, whoever merges, so the result does not depend on which CTA arrived last.
+constexpr int kMergeBatch = 9;
+__device__ __forceinline__ void merge_rows(const float* base, int count, int own, float om, float ol, const float (&oacc)[8],
+                                           int hh, int sub, float& mx, float& lsum, float (&acc)[8]) {
   mx = -INFINITY;
   lsum = 0.f;
 #pragma unroll
   for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-  for (int q0 = 0; q0 < count; q0 += 8) {
-    float2 ml[8];
-    float4 va[8], vb[8];
+  for (int q0 = 0; q0 < count; q0 += kMergeBatch) {
+    float2 ml[kMergeBatch];
+    float4 va[kMergeBatch], vb[kMergeBatch];
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
-      const int q = min(q0 + k, count - 1);
-      const float* row = base + (size_t)q * kSlotFloats + hh * kRowFloats;
-      ml[k] = __ldcg(reinterpret_cast<const float2*>(row));
-      va[k] = __ldcg(reinterpret_cast<const float4*>(row + 4 + 8 * sub));
-      vb[k] = __ldcg(reinterpret_cast<const float4*>(row + 8 + 8 * sub));
+    for (int k = 0; k < kMergeBatch; ++k) {
+      const int q = q0 + k;
+      if (q == own) {
+        ml[k] = make_float2(om, ol);
+        va[k] = make_float4(oacc[0], oacc[1], oacc[2], oacc[3]);
+        vb[k] = make_float4(oacc[4], oacc[5], oacc[6], oacc[7]);
+      } else {
+        const float* row = base + (size_t)min(q, count - 1) * kSlotFloats + hh * kRowFloats;
+        ml[k] = __ldcg(reinterpret_cast<const float2*>(row));
+        va[k] = __ldcg(reinterpret_cast<const float4*>(row + 4 + 8 * sub));
+        vb[k] = __ldcg(reinterpret_cast<const float4*>(row + 8 + 8 * sub));
+      }
     }
     float bm = mx;   // running reference point: rescale what is already accumulated when a batch raises it
 #pragma unroll
-    for (int k = 0; k < 8; ++k) bm = fmaxf(bm, (q0 + k < count) ? ml[k].x : -INFINITY);
+    for (int k = 0; k < kMergeBatch; ++k) bm = fmaxf(bm, (q0 + k < count) ? ml[k].x : -INFINITY);
     if (bm > mx) {
       const float f = mx == -INFINITY ? 0.f : ex2_approx(mx - bm);
       lsum *= f;
@@ -250,7 +259,7 @@ __device__ __forceinline__ void merge_rows(const float* base, int count, int hh,
       mx = bm;
     }
 #pragma unroll
-    for (int k = 0; k < 8; ++k) {
+    for (int k = 0; k < kMergeBatch; ++k) {
       const float w = (q0 + k < count && ml[k].x != -INFINITY) ? ex2_approx(ml[k].x - mx) : 0.f;
       acc[0] += w * va[k].x; acc[1] += w * va[k].y; acc[2] += w * va[k].z; acc[3] += w * va[k].w;
       acc[4] += w * vb[k].x; acc[5] += w * vb[k].y; acc[6] += w * vb[k].z; acc[7] += w * vb[k].w;
@@ -641,6 +650,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const __gr
     float* slot = p.partials + ((size_t)bh * p.parts_cap + (cta - part0)) * kSlotFloats;
     static_assert(kNW >= 6, "warps 4 and 5 carry the request counter and the appended rows");
     const bool worker = threadIdx.x < 128;   // warps 0-3 carry the merge protocol; the others only meet the barriers
+    float own_m = -INFINITY, own_l = 0.f, own_acc[8] = {0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f, 0.f};   // this CTA's partial
     if (worker) {
       const int hh = threadIdx.x >> 4, sub = threadIdx.x & 15;  // 16 threads per head, 8 dims each
       float mw[kNW], mx = -INFINITY;
@@ -662,6 +672,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const __gr
       __stcg(reinterpret_cast<float4*>(orow + 4 + 8 * sub), a0);
       __stcg(reinterpret_cast<float4*>(orow + 8 + 8 * sub), a1);
       if (sub == 0) __stcg(reinterpret_cast<float2*>(orow), make_float2(mx, lsum));
+      own_m = mx; own_l = lsum;
+      own_acc[0] = a0.x; own_acc[1] = a0.y; own_acc[2] = a0.z; own_acc[3] = a0.w;
+      own_acc[4] = a1.x; own_acc[5] = a1.y; own_acc[6] = a1.z; own_acc[7] = a1.w;
     }
     // ---- two-level exact merge: groups of 32 partials, then the group results ----
     // Release pattern: the CTA barrier orders every thread's partial stores before thread 0's fence, whose
@@ -681,7 +694,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const __gr
     named_bar_sync(1, kConsumers);
     bool last = flags[0] != 0;
     if (last) {
-      if (worker) merge_rows(p.partials + ((size_t)bh * p.parts_cap + 32 * grp) * kSlotFloats, gsize, hh, sub, mx, lsum, acc);
+      if (worker)
+        merge_rows(p.partials + ((size_t)bh * p.parts_cap + 32 * grp) * kSlotFloats, gsize, part & 31, own_m, own_l, own_acc, hh,
+                   sub, mx, lsum, acc);
       if (ngroups > 1) {
         if (worker) store_row(p.group_partials + ((size_t)bh * p.groups_cap + grp) * kSlotFloats, hh, sub, mx, lsum, acc);
         named_bar_sync(1, kConsumers);
@@ -694,7 +709,13 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const __gr
         }
         named_bar_sync(1, kConsumers);
         last = flags[1] != 0;
-        if (last && worker) merge_rows(p.group_partials + (size_t)bh * p.groups_cap * kSlotFloats, ngroups, hh, sub, mx, lsum, acc);
+        if (last && worker) {   // this CTA's own group result is still in (mx, lsum, acc)
+          const float gm = mx, gl = lsum;
+          float gacc[8];
+#pragma unroll
+          for (int e = 0; e < 8; ++e) gacc[e] = acc[e];
+          merge_rows(p.group_partials + (size_t)bh * p.groups_cap * kSlotFloats, ngroups, grp, gm, gl, gacc, hh, sub, mx, lsum, acc);
+        }
       }
     }
     if (last) {
