@@ -560,6 +560,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const __gr
     const int rlen0 = *reinterpret_cast<const int*>((const uint8_t*)p.v.recent_len + (size_t)b * p.v.recent_len_bstride);
     const int rlen = rlen0 + (has_append ? 1 : 0);
     state_reset(st);
+    // who else works on this head: known before the first tile arrives, so it is off the path to the merge
+    const int part0 = first_cta_of(p, bh);
+    const int nparts = last_cta_of(p, bh) - part0 + 1;
 
     // query fragments of head g of this KV group, channels 32t..32t+31
     const uint16_t* qrow = nullptr;
@@ -645,8 +648,6 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const __gr
       if (g == 0) { r0[0] = st.m[0]; r0[1] = st.l[0]; r1[0] = st.m[1]; r1[1] = st.l[1]; }
     }
     named_bar_sync(1, kConsumers);
-    const int part0 = first_cta_of(p, bh);
-    const int nparts = last_cta_of(p, bh) - part0 + 1;
     float* slot = p.partials + ((size_t)bh * p.parts_cap + (cta - part0)) * kSlotFloats;
     static_assert(kNW >= 6, "warps 4 and 5 carry the request counter and the appended rows");
     const bool worker = threadIdx.x < 128;   // warps 0-3 carry the merge protocol; the others only meet the barriers
