@@ -327,6 +327,7 @@ def sharded_1m(device, rank, world, steps, warmup, dist_on):
         us, graphed, steps = timed(lambda: ex(q), steps)
     else:
         gathered = R.SequenceShardedExecutor(ex)
+        local_us, _, _ = timed(lambda: ex.decode_state(q, out=gathered.state), steps)   # this rank's shard alone
         nccl_us, _, _ = timed(lambda: gathered(q), steps)
         # the fused variant is the one reported; if it cannot be set up or times out on this box, every rank
         # agrees on that and the all-gather number is reported instead (with the reason)
@@ -354,6 +355,7 @@ def sharded_1m(device, rank, world, steps, warmup, dist_on):
            "launches_per_step": 1, "cuda_graph": graphed}
     if nccl_us is not None:
         out["us_per_step_nccl_all_gather"] = round(nccl_us, 2)
+        out["us_per_step_local_shard_only"] = round(local_us, 2)
         if fused_error:
             out.update(collective="nccl all_gather of [Hq,130] fp32 per rank", launches_per_step=2, fused_error=fused_error)
     return out

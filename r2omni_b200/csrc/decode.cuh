@@ -42,6 +42,10 @@ constexpr int kSlotFloats = 8 * kRowFloats;      // one partial: 8 heads of a KV
 constexpr int kScratchBytes = kNW * kSlotFloats * 4;
 constexpr int kSmemBytes = kStages * kStageBytes + kScratchBytes + 256;
 
+// Partials of a (request, kv head) are merged in groups of kMergeGroup by each group's last-arriving CTA, then the
+// group results by the head's last arriver.  A group is one batch of loads for the merging CTA (merge_rows), so
+// both levels cost one dependent round trip to memory for up to kMergeGroup * kMergeGroup CTAs per head.
+constexpr int kMergeGroup = 9;
 constexpr int kWsHeaderBytes = 256;
 
 struct DecodeParams {

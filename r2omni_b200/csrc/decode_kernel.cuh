@@ -224,7 +224,7 @@ __device__ __forceinline__ void produce_full_tile(const DecodeParams& p, const T
 // Row `own` (or -1) is not loaded: the caller still holds it in registers (om, ol, oacc), which saves the merging
 // CTA a dependent round trip to memory for the common nine-partial head.  Rows are folded in slot order in
 // batches of nine slots, whoever merges, so the result does not depend on which CTA arrived last.
-constexpr int kMergeBatch = 9;
+constexpr int kMergeBatch = kMergeGroup;
 __device__ __forceinline__ void merge_rows(const float* base, int count, int own, float om, float ol, const float (&oacc)[8],
                                            int hh, int sub, float& mx, float& lsum, float (&acc)[8]) {
   mx = -INFINITY;
@@ -677,12 +677,12 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const __gr
       own_acc[0] = a0.x; own_acc[1] = a0.y; own_acc[2] = a0.z; own_acc[3] = a0.w;
       own_acc[4] = a1.x; own_acc[5] = a1.y; own_acc[6] = a1.z; own_acc[7] = a1.w;
     }
-    // ---- two-level exact merge: groups of 32 partials, then the group results ----
+    // ---- two-level exact merge: groups of kMergeGroup partials, then the group results ----
     // Release pattern: the CTA barrier orders every thread's partial stores before thread 0's fence, whose
     // cumulativity publishes them before the ticket; the reader side mirrors it (ticket, fence, barrier).
     const int hh = (threadIdx.x >> 4) & 7, sub = threadIdx.x & 15;
-    const int part = cta - part0, grp = part >> 5, ngroups = (nparts + 31) >> 5;
-    const int gsize = min(32, nparts - 32 * grp);
+    const int part = cta - part0, grp = part / kMergeGroup, ngroups = (nparts + kMergeGroup - 1) / kMergeGroup;
+    const int gsize = min(kMergeGroup, nparts - kMergeGroup * grp);
     float mx, lsum, acc[8];
     named_bar_sync(1, kConsumers);
     if (threadIdx.x == 0) {
@@ -696,7 +696,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const __gr
     bool last = flags[0] != 0;
     if (last) {
       if (worker)
-        merge_rows(p.partials + ((size_t)bh * p.parts_cap + 32 * grp) * kSlotFloats, gsize, part & 31, own_m, own_l, own_acc, hh,
+        merge_rows(p.partials + ((size_t)bh * p.parts_cap + kMergeGroup * grp) * kSlotFloats, gsize, part - kMergeGroup * grp, own_m, own_l,
+                   own_acc, hh,
                    sub, mx, lsum, acc);
       if (ngroups > 1) {
         if (worker) store_row(p.group_partials + ((size_t)bh * p.groups_cap + grp) * kSlotFloats, hh, sub, mx, lsum, acc);

@@ -106,7 +106,7 @@ int derive(const R2KGeom* g, DecodeParams* p) {
   if (p->grid >= 2 * p->bh_total) p->grid = p->grid / p->bh_total * p->bh_total;
   if ((int64_t)p->grid * p->bh_total >= (int64_t)1 << 31) return R2K_ERR_GEOMETRY;
   p->parts_cap = (p->grid + p->bh_total - 1) / p->bh_total + 1;
-  p->groups_cap = (p->parts_cap + 31) / 32;
+  p->groups_cap = (p->parts_cap + kMergeGroup - 1) / kMergeGroup;
   p->groups2 = g2;
   p->group2_shift = ilog2(g->v2_group);
   p->kblock_shift = ilog2(g->k_block);
