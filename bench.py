@@ -351,7 +351,7 @@ def sharded_1m(device, rank, world, steps, warmup, dist_on):
         dist.all_reduce(bytes_all)
     out = {"workload": "sharded_1m_b1", "tokens": total, "n_gpus": world, "us_per_step": round(us, 2),
            "gbps": round(float(bytes_all.item()) / (us * 1e-6) / 1e9, 1), "steps": steps,
-           "collective": "none" if world == 1 else "fused: peer stores + flags inside the decode launch",
+           "collective": "none" if world == 1 else "fused: tagged peer stores over NVLink inside the decode launch",
            "launches_per_step": 1, "cuda_graph": graphed}
     if nccl_us is not None:
         out["us_per_step_nccl_all_gather"] = round(nccl_us, 2)

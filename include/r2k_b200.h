@@ -196,9 +196,9 @@ int r2k_merge_states(const float* states, int32_t num_states, int64_t state_stri
  * One exchange buffer per rank (GPU), mapped into every rank's address space.
  * A decode launched through r2k_decode_exchange ends, for every (request, kv
  * head), by storing this rank's un-normalised state rows into EVERY rank's
- * buffer over NVLink (plain peer stores), publishing a step flag, waiting
- * (bounded) for the other ranks' flags in its own buffer and merging all
- * ranks' rows there -- the exact merge of r2k_merge_states.  Every rank ends
+ * buffer over NVLink (plain peer stores of 8-byte (value, step) words), waiting
+ * (bounded) until all ranks' words of this step have landed in its own buffer
+ * and merging them there -- the exact merge of r2k_merge_states.  Every rank ends
  * with the same output; there is no collective launch and no merge launch.
  * No counterpart in the reference (it has no multi-GPU path); the arithmetic
  * is _merge_state, r2omni/sspa/kernels/triton_fourq_attention.py:58-69.

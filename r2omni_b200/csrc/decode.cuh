@@ -77,8 +77,8 @@ struct DecodeParams {
   // swizzle: full value tiles arrive bank-conflict-free for the value MMA's loads (valid when fp_tma != 0)
   int fp_tma;
   // fused cross-rank merge (xw > 1): every rank's exchange buffer, this rank, the world size and the step counter.
-  // A buffer holds two halves (step parity) of [world][rows][130] float state rows, then two halves of
-  // [world][bh_total] step flags at byte offset xflags_off.
+  // A buffer holds two halves (step parity) of [world][rows][130] (value, step) words, then the device-side step
+  // counter at byte offset xflags_off.
   int xw, xrank;
   uint32_t xseq, xflags_off;
   float* xbuf[R2K_MAX_RANKS];

@@ -328,10 +328,10 @@ __device__ __forceinline__ void write_output(const DecodeParams& p, size_t orow,
 }
 
 // Step counter of the fused cross-rank merge: given by the host, or (xseq == 0) kept on the device behind the
-// flags of this rank's exchange buffer, so that a captured graph can be replayed.  Every reader sees the value
+// state words of this rank's exchange buffer, so that a captured graph can be replayed.  Every reader sees the value
 // of the previous step; the CTA that finishes last moves it on at the very end of the kernel.
 __device__ __forceinline__ uint32_t* exchange_counter(const DecodeParams& p) {
-  return reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(p.xbuf[p.xrank]) + p.xflags_off) + (size_t)2 * p.xw * p.bh_total;
+  return reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(p.xbuf[p.xrank]) + p.xflags_off);
 }
 __device__ __forceinline__ uint32_t exchange_step(const DecodeParams& p) {
   if (p.xseq != 0) return p.xseq;
@@ -339,65 +339,73 @@ __device__ __forceinline__ uint32_t exchange_step(const DecodeParams& p) {
   return s == 0 ? 1u : s;
 }
 
-// Fused cross-rank merge of one (request, kv head), run by the head's last-arriving CTA on every rank: push this
-// rank's un-normalised rows into every rank's exchange buffer (plain peer stores), publish the step flag behind a
-// system-scope fence, wait (bounded) for every rank's flag in the local buffer, merge the local copies in rank
-// order.  On return (lsum, acc) hold the merged state; the caller normalises and stores as usual.
+// Fused cross-rank merge of one (request, kv head), run by the head's last-arriving CTA on every rank.  Every
+// state value travels as an 8-byte (value, step) word: the 128 worker threads store this rank's rows into every
+// rank's exchange buffer (plain peer stores over NVLink), then poll the words of their own channels in the local
+// buffer until all carry this step's tag (bounded), and fold the ranks' rows in rank order.  No fence, no
+// separate flag, no barrier.  A buffer holds two halves (step parity) of [world][rows][130] words; the tag makes a
+// stale word of an older step unmistakable.  On return (lsum, acc) hold the merged state; the caller normalises
+// and stores as usual.
 // Not inlined: it runs once per (request, kv head) and must not cost the streaming loop any registers.
-__device__ __noinline__ void exchange_merge(const DecodeParams& p, uint32_t seq, int bh, size_t orow, bool valid,
-                                               bool worker, int sub, float mx, float& lsum, float (&acc)[8]) {
+__device__ __noinline__ void exchange_merge(const DecodeParams& p, uint32_t seq, size_t orow, bool valid, bool worker, int sub,
+                                               float mx, float& lsum, float (&acc)[8]) {
+  if (!worker || !valid) return;
   const uint32_t par = seq & 1u;
   const size_t rows = (size_t)p.g.batch * p.g.num_q_heads;
-  if (worker && valid) {
-    const size_t off = ((size_t)(par * p.xw + p.xrank) * rows + orow) * 130;
-    for (int r = 0; r < p.xw; ++r) {
-      float* o = p.xbuf[r] + off;
-      if (sub == 0) *reinterpret_cast<float2*>(o) = make_float2(mx * kLn2, lsum);
-#pragma unroll
-      for (int e = 0; e < 8; e += 2) *reinterpret_cast<float2*>(o + 2 + 8 * sub + e) = make_float2(acc[e], acc[e + 1]);
+  const size_t mine = ((size_t)(par * p.xw + p.xrank) * rows + orow) * 130;
+  for (int r = 0; r < p.xw; ++r) {
+    uint2* o = reinterpret_cast<uint2*>(p.xbuf[r]) + mine;
+    if (sub == 0) {
+      st_tagged_sys(o, __float_as_uint(mx * kLn2), seq);
+      st_tagged_sys(o + 1, __float_as_uint(lsum), seq);
     }
-  }
-  named_bar_sync(1, kConsumers);
-  const size_t flag_index = (size_t)(par * p.xw) * p.bh_total + bh;
-  if (threadIdx.x == 0) {
-    __threadfence_system();
-    for (int r = 0; r < p.xw; ++r)
-      st_relaxed_sys(reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(p.xbuf[r]) + p.xflags_off) + flag_index +
-                         (size_t)p.xrank * p.bh_total,
-                     seq);
-  }
-  if ((int)threadIdx.x < p.xw) {
-    const uint32_t* f = reinterpret_cast<const uint32_t*>(reinterpret_cast<const uint8_t*>(p.xbuf[p.xrank]) + p.xflags_off) +
-                        flag_index + (size_t)threadIdx.x * p.bh_total;
-    bool arrived = false;
-    for (uint32_t i = 0; i < (1u << 16) && !arrived; ++i) {
-      arrived = ld_acquire_sys(f) == seq;
-      if (!arrived) __nanosleep(i < 256 ? 100 : 20000);   // about 1.3 s in all: ranks may be skewed by host work
-    }
-    if (!arrived) atomicExch(p.err, R2K_ERR_DEVICE_TIMEOUT);
-  }
-  named_bar_sync(1, kConsumers);
-  if (worker && valid) {
-    const float* base = p.xbuf[p.xrank] + ((size_t)(par * p.xw) * rows + orow) * 130;
-    float m_all = -INFINITY;
-    for (int s = 0; s < p.xw; ++s) m_all = fmaxf(m_all, __ldcg(base + (size_t)s * rows * 130));
-    float l = 0.f;
 #pragma unroll
-    for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-    for (int s = 0; s < p.xw; ++s) {
-      const float* row = base + (size_t)s * rows * 130;
-      const float2 ml = __ldcg(reinterpret_cast<const float2*>(row));
-      const float wgt = (ml.x == -INFINITY) ? 0.f : __expf(ml.x - m_all);
-#pragma unroll
-      for (int e = 0; e < 8; e += 2) {
-        const float2 v = __ldcg(reinterpret_cast<const float2*>(row + 2 + 8 * sub + e));
-        acc[e] += wgt * v.x;
-        acc[e + 1] += wgt * v.y;
-      }
-      l += wgt * ml.y;
-    }
-    lsum = l;
+    for (int e = 0; e < 8; ++e) st_tagged_sys(o + 2 + 8 * sub + e, __float_as_uint(acc[e]), seq);
   }
+  const uint2* base = reinterpret_cast<const uint2*>(p.xbuf[p.xrank]) + ((size_t)(par * p.xw) * rows + orow) * 130;
+  float m_all = -INFINITY, l = 0.f;
+  float ms[R2K_MAX_RANKS], ls[R2K_MAX_RANKS];
+  bool timed_out = false;
+  // pass 1: every rank's (max, sum) -- the reference point needs all of them
+  for (int s = 0; s < p.xw; ++s) {
+    const uint2* row = base + (size_t)s * rows * 130;
+    uint2 a = ld_tagged_sys(row), c = ld_tagged_sys(row + 1);
+    for (uint32_t i = 0; (a.y != seq || c.y != seq) && i < (1u << 16); ++i) {
+      __nanosleep(i < 256 ? 100 : 20000);   // about 1.3 s in all: ranks may be skewed by host work
+      a = ld_tagged_sys(row);
+      c = ld_tagged_sys(row + 1);
+    }
+    if (a.y != seq || c.y != seq) timed_out = true;
+    ms[s] = __uint_as_float(a.x);
+    ls[s] = __uint_as_float(c.x);
+    m_all = fmaxf(m_all, ms[s]);
+  }
+#pragma unroll
+  for (int e = 0; e < 8; ++e) acc[e] = 0.f;
+  // pass 2: this thread's eight channels of every rank, folded in rank order
+  for (int s = 0; s < p.xw; ++s) {
+    const uint2* row = base + (size_t)s * rows * 130 + 2 + 8 * sub;
+    uint2 v[8];
+#pragma unroll
+    for (int e = 0; e < 8; ++e) v[e] = ld_tagged_sys(row + e);
+    for (uint32_t i = 0; i < (1u << 16); ++i) {
+      bool ok = true;
+#pragma unroll
+      for (int e = 0; e < 8; ++e) ok = ok && v[e].y == seq;
+      if (ok) break;
+      __nanosleep(i < 256 ? 100 : 20000);
+#pragma unroll
+      for (int e = 0; e < 8; ++e) v[e] = ld_tagged_sys(row + e);
+    }
+#pragma unroll
+    for (int e = 0; e < 8; ++e) timed_out = timed_out || v[e].y != seq;
+    const float wgt = (ms[s] == -INFINITY) ? 0.f : __expf(ms[s] - m_all);
+#pragma unroll
+    for (int e = 0; e < 8; ++e) acc[e] += wgt * __uint_as_float(v[e].x);
+    l += wgt * ls[s];
+  }
+  if (timed_out) atomicExch(p.err, R2K_ERR_DEVICE_TIMEOUT);
+  lsum = l;
 }
 
 // One warp's 32-token key block of a tile: scores, softmax update, value accumulation.
@@ -750,7 +758,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const __gr
             __ldg(reinterpret_cast<const uint2*>((const uint8_t*)p.app_v + src));
       }
       const size_t orow = (size_t)b * p.g.num_q_heads + h * p.gqa + hh;
-      if (p.xw > 1) exchange_merge(p, exchange_step(p), bh, orow, hh < p.gqa, worker, sub, mx, lsum, acc);
+      if (p.xw > 1) exchange_merge(p, exchange_step(p), orow, hh < p.gqa, worker, sub, mx, lsum, acc);
       if (worker) write_output<BF16>(p, orow, hh < p.gqa, sub, mx, lsum, acc);
     }
     named_bar_sync(1, kConsumers);  // scratch and flags are reused by the next (request, kv head)

@@ -133,6 +133,16 @@ __device__ __forceinline__ uint32_t ld_acquire_sys(const uint32_t* p) {
 __device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) {
   asm volatile("st.relaxed.sys.global.u32 [%0], %1;\n" ::"l"(p), "r"(v) : "memory");
 }
+// One 8-byte word = (payload, step tag), written and read as a single transaction: the reader accepts the
+// payload when the tag matches, so no fence and no separate flag stand between a peer store and its use.
+__device__ __forceinline__ void st_tagged_sys(uint2* p, uint32_t payload, uint32_t tag) {
+  asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};\n" ::"l"(p), "r"(payload), "r"(tag) : "memory");
+}
+__device__ __forceinline__ uint2 ld_tagged_sys(const uint2* p) {
+  uint2 v;
+  asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
+  return v;
+}
 
 __device__ __forceinline__ void named_bar_sync(int id, int threads) {
   asm volatile("bar.sync %0, %1;\n" ::"r"(id), "r"(threads) : "memory");

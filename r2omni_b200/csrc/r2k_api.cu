@@ -272,7 +272,7 @@ int r2k_decode_workspace_init(void* workspace, size_t bytes, void* stream) {
 }
 
 static size_t exchange_states_bytes(const R2KGeom* g, int world) {
-  const size_t n = (size_t)2 * world * g->batch * g->num_q_heads * 130 * sizeof(float);
+  const size_t n = (size_t)2 * world * g->batch * g->num_q_heads * 130 * sizeof(uint2);   // (value, step) words
   return (n + 127) / 128 * 128;
 }
 
@@ -381,8 +381,7 @@ int r2k_exchange_bytes(const R2KGeom* geom, int32_t world, size_t* bytes) {
   int rc = check_geom(geom);
   if (rc) return rc;
   if (world < 1 || world > R2K_MAX_RANKS) return R2K_ERR_GEOMETRY;
-  const size_t flags = (size_t)2 * world * geom->batch * geom->num_kv_heads * sizeof(uint32_t);
-  *bytes = exchange_states_bytes(geom, world) + (flags + 127) / 128 * 128 + 128;   // + device step counter
+  *bytes = exchange_states_bytes(geom, world) + 128;   // + device step counter
   return R2K_OK;
 }
 

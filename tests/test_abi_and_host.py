@@ -78,8 +78,8 @@ def test_exchange_entry_points_validate_without_a_gpu(lib):
     g.page_size, g.k_block, g.v2_group, g.recent_capacity, g.sm_scale = 64, 32, 32, 128, 0.0
     need = C.c_size_t(0)
     assert lib.r2k_exchange_bytes(C.byref(g), 4, C.byref(need)) == L.OK
-    states = 2 * 4 * 2 * 16 * 130 * 4
-    assert need.value == (states + 127) // 128 * 128 + 128 + 128   # states, 2 x 4 x 4 flags rounded up, step counter
+    states = 2 * 4 * 2 * 16 * 130 * 8   # two halves x ranks x rows x (value, step) words
+    assert need.value == (states + 127) // 128 * 128 + 128          # + the device-side step counter
     assert lib.r2k_exchange_bytes(C.byref(g), 9, C.byref(need)) == L.ERR_GEOMETRY
     assert lib.r2k_exchange_bytes(C.byref(g), 2, None) == L.ERR_NULL
     assert lib.r2k_decode_exchange(C.byref(g), None, None, None, None, 0, None, 0, None, None) == L.ERR_NULL
