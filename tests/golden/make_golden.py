@@ -2,7 +2,7 @@
 
 Run once, in a container that has the reference checkout (read-only):
 
-    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py [/path/to/R2-Omni]
+    PYTHONDONTWRITEBYTECODE=1 python tests/golden/make_golden.py /path/to/R2-Omni
 
 It imports the unmodified reference (CPU torch path), builds small caches from
 seeded inputs, appends tokens through the reference's own flush state machine,
@@ -18,7 +18,9 @@ import sys
 import numpy as np
 import torch
 
-REF = sys.argv[1] if len(sys.argv) > 1 else "/root/reference"
+if len(sys.argv) < 2 and "R2OMNI_REFERENCE" not in os.environ:
+    raise SystemExit("usage: make_golden.py /path/to/R2-Omni   (or set R2OMNI_REFERENCE)")
+REF = sys.argv[1] if len(sys.argv) > 1 else os.environ["R2OMNI_REFERENCE"]
 sys.path.insert(0, REF)
 sys.dont_write_bytecode = True
 
