@@ -334,9 +334,15 @@ def sharded_1m(device, rank, world, steps, warmup, dist_on):
         fused_error, fused = None, None
         try:
             fused = R.SequenceShardedExecutor(ex, fused=True, device_step_counter=True)
-            us, graphed, steps = timed(lambda: fused(q), steps)
-            if ex.device_status() != 0:
+            fused(q)                                   # one step first: a broken exchange shows up as a bounded
+            probe = torch.tensor([float(ex.device_status())], device=device)   # wait here, not 300 times over
+            dist.all_reduce(probe, op=dist.ReduceOp.MAX)
+            if float(probe.item()) != 0.0:
                 fused_error = "device-side timeout in the cross-rank wait"
+            else:
+                us, graphed, steps = timed(lambda: fused(q), steps)
+                if ex.device_status() != 0:
+                    fused_error = "device-side timeout in the cross-rank wait"
         except Exception as exc:   # noqa: BLE001 -- reported in the JSON line
             fused_error = repr(exc)[:200]
         ok = torch.tensor([0.0 if fused_error else 1.0], device=device)
