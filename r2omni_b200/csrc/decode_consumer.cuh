@@ -88,13 +88,16 @@ __device__ __forceinline__ void softmax_update(WarpState& st, float (&s)[NT][4])
     mx0 = fmaxf(mx0, fmaxf(s[j][0], s[j][2]));
     mx1 = fmaxf(mx1, fmaxf(s[j][1], s[j][3]));
   }
-  mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 4));
-  mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 4));
-  mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 8));
-  mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 8));
-  mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 16));
-  mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 16));
+  // The reference point is the same in all eight lanes that share a head pair, so each lane can test its own
+  // scores against it; the cross-lane maximum is only needed when some lane asks for a move (about one block in
+  // ten), which keeps six shuffles and their latency out of the common path.
   if (__any_sync(0xffffffffu, (mx0 > st.m[0] + 8.f) | (mx1 > st.m[1] + 8.f))) {
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 4));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 4));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 8));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 8));
+    mx0 = fmaxf(mx0, __shfl_xor_sync(0xffffffffu, mx0, 16));
+    mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 16));
     const float n0 = fmaxf(st.m[0], mx0), n1 = fmaxf(st.m[1], mx1);
     const float f0 = ex2_approx(st.m[0] - n0), f1 = ex2_approx(st.m[1] - n1);  // m = -inf -> 0
     st.l[0] *= f0; st.l[1] *= f1; st.lp[0] *= f0; st.lp[1] *= f1;
