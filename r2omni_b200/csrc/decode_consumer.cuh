@@ -56,14 +56,16 @@ __device__ __forceinline__ int pi_row(int r) {  // r in 0..7
 struct WarpState {
   float m[2];      // running reference point (log2 units) of heads 2t, 2t+1
   float l[2];      // this lane's share of sum-exp
-  float lp[2];     // this lane's share of sum of fp16(p * scale) over INT4-value tokens (for the +8 code offset)
+  float corr[4];   // 8 * 2^-24 * sum of fp16(p * scale) over INT4-value tokens (the +8 code offset), accumulated by
+                   // one MMA per tile whose A rows are all 8: complete per lane, [0],[2] head 2t and [1],[3] head 2t+1
   float o[8][4];   // O^T fragments: block j <-> dims 16g+2j (c0,c1) and 16g+2j+1 (c2,c3); columns = heads 2t,2t+1
   int units;       // 0: true units; 1: INT4 units (even dims * 2^-24, odd dims * 2^-20)
 };
 
 __device__ __forceinline__ void state_reset(WarpState& s) {
   s.m[0] = s.m[1] = -INFINITY;
-  s.l[0] = s.l[1] = s.lp[0] = s.lp[1] = 0.f;
+  s.l[0] = s.l[1] = 0.f;
+  s.corr[0] = s.corr[1] = s.corr[2] = s.corr[3] = 0.f;
 #pragma unroll
   for (int j = 0; j < 8; ++j) s.o[j][0] = s.o[j][1] = s.o[j][2] = s.o[j][3] = 0.f;
   s.units = 0;
@@ -100,7 +102,8 @@ __device__ __forceinline__ void softmax_update(WarpState& st, float (&s)[NT][4])
     mx1 = fmaxf(mx1, __shfl_xor_sync(0xffffffffu, mx1, 16));
     const float n0 = fmaxf(st.m[0], mx0), n1 = fmaxf(st.m[1], mx1);
     const float f0 = ex2_approx(st.m[0] - n0), f1 = ex2_approx(st.m[1] - n1);  // m = -inf -> 0
-    st.l[0] *= f0; st.l[1] *= f1; st.lp[0] *= f0; st.lp[1] *= f1;
+    st.l[0] *= f0; st.l[1] *= f1;
+    st.corr[0] *= f0; st.corr[1] *= f1; st.corr[2] *= f0; st.corr[3] *= f1;
 #pragma unroll
     for (int j = 0; j < 8; ++j) { st.o[j][0] *= f0; st.o[j][1] *= f1; st.o[j][2] *= f0; st.o[j][3] *= f1; }
     st.m[0] = n0; st.m[1] = n1;
@@ -206,13 +209,8 @@ __device__ __forceinline__ void pv_int4(WarpState& st, uint32_t sb, const LaneOf
     if (16 * j + pg + 8 < lo || 16 * j + pg + 8 >= hi) sc = 0.f;
   }
   const uint32_t ha = pack_f16x2(p[0] * sa, p[1] * sa), hb = pack_f16x2(p[2] * sc, p[3] * sc);
-  {
-    const float2 fa = __half22float2(*reinterpret_cast<const __half2*>(&ha));
-    const float2 fb = __half22float2(*reinterpret_cast<const __half2*>(&hb));
-    st.lp[0] += fa.x + fb.x;
-    st.lp[1] += fa.y + fb.y;
-  }
   const uint32_t b0 = movmatrix_trans(ha), b1 = movmatrix_trans(hb);
+  mma_f16(st.corr, 0x00080008u, 0x00080008u, 0x00080008u, 0x00080008u, b0, b1);   // the offset the codes carry below
   const uint2 w0 = lds64(sb + o.va + 1024 * j), w1 = lds64(sb + o.vb + 1024 * j);
   const uint2 w2 = lds64(sb + o.va + 1024 * j + 512), w3 = lds64(sb + o.vb + 1024 * j + 512);
   constexpr uint32_t kFixLo = 0x00080008u, kFixHi = 0x00800080u;

@@ -640,14 +640,12 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const __gr
     for (int d = 4; d < 32; d <<= 1) {
       st.l[0] += __shfl_xor_sync(0xffffffffu, st.l[0], d);
       st.l[1] += __shfl_xor_sync(0xffffffffu, st.l[1], d);
-      st.lp[0] += __shfl_xor_sync(0xffffffffu, st.lp[0], d);
-      st.lp[1] += __shfl_xor_sync(0xffffffffu, st.lp[1], d);
     }
     {
       float* mine = scratch + warp * kSlotFloats;
       float* r0 = mine + (2 * t) * kRowFloats;
       float* r1 = r0 + kRowFloats;
-      const float c0 = 8.f * st.lp[0], c1 = 8.f * st.lp[1];  // INT4 value codes were fed as code+8
+      const float c0 = st.corr[0] * k2p24, c1 = st.corr[1] * k2p24;  // INT4 value codes were fed as code+8
 #pragma unroll
       for (int j = 0; j < 8; ++j) {
         *reinterpret_cast<float2*>(r0 + 4 + 16 * g + 2 * j) = make_float2(st.o[j][0] - c0, st.o[j][2] - c0);
