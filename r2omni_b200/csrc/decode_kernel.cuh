@@ -363,46 +363,65 @@ __device__ __noinline__ void exchange_merge(const DecodeParams& p, uint32_t seq,
     for (int e = 0; e < 8; ++e) st_tagged_sys(o + 2 + 8 * sub + e, __float_as_uint(acc[e]), seq);
   }
   const uint2* base = reinterpret_cast<const uint2*>(p.xbuf[p.xrank]) + ((size_t)(par * p.xw) * rows + orow) * 130;
+  const size_t pitch = rows * 130;   // words between two ranks' copies of this row
   float m_all = -INFINITY, l = 0.f;
-  float ms[R2K_MAX_RANKS], ls[R2K_MAX_RANKS];
   bool timed_out = false;
-  // pass 1: every rank's (max, sum) -- the reference point needs all of them
-  for (int s = 0; s < p.xw; ++s) {
-    const uint2* row = base + (size_t)s * rows * 130;
-    uint2 a = ld_tagged_sys(row), c = ld_tagged_sys(row + 1);
-    for (uint32_t i = 0; (a.y != seq || c.y != seq) && i < (1u << 16); ++i) {
-      __nanosleep(i < 256 ? 100 : 20000);   // about 1.3 s in all: ranks may be skewed by host work
-      a = ld_tagged_sys(row);
-      c = ld_tagged_sys(row + 1);
+  // pass 1: every rank's maximum -- the reference point needs all of them.  Four ranks' loads are in flight
+  // together: polling rank after rank would pay one memory latency per rank.
+#pragma unroll 1
+  for (int s0 = 0; s0 < p.xw; s0 += 4) {
+    uint4 h[4];
+    bool ok = false;
+    for (uint32_t i = 0; i < (1u << 16) && !ok; ++i) {
+      if (i) __nanosleep(i < 256 ? 100 : 20000);   // about 1.3 s in all: ranks may be skewed by host work
+#pragma unroll
+      for (int k = 0; k < 4; ++k) h[k] = ld_tagged2_sys(base + (size_t)min(s0 + k, p.xw - 1) * pitch);
+      ok = true;
+#pragma unroll
+      for (int k = 0; k < 4; ++k) ok = ok && h[k].y == seq && h[k].w == seq;
     }
-    if (a.y != seq || c.y != seq) timed_out = true;
-    ms[s] = __uint_as_float(a.x);
-    ls[s] = __uint_as_float(c.x);
-    m_all = fmaxf(m_all, ms[s]);
+    timed_out = timed_out || !ok;
+#pragma unroll
+    for (int k = 0; k < 4; ++k) m_all = fmaxf(m_all, __uint_as_float(h[k].x));
   }
 #pragma unroll
   for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-  // pass 2: this thread's eight channels of every rank, folded in rank order
-  for (int s = 0; s < p.xw; ++s) {
-    const uint2* row = base + (size_t)s * rows * 130 + 2 + 8 * sub;
-    uint2 v[8];
+  // pass 2: (max, sum) again and this thread's eight channels, two ranks in flight at a time (more would cost
+  // registers), folded in rank order
+#pragma unroll 1
+  for (int s0 = 0; s0 < p.xw; s0 += 2) {
+    uint4 h[2], v[2][4];
+    bool ok = false;
+    for (uint32_t i = 0; i < (1u << 16) && !ok; ++i) {
+      if (i) __nanosleep(i < 256 ? 100 : 20000);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) v[e] = ld_tagged_sys(row + e);
-    for (uint32_t i = 0; i < (1u << 16); ++i) {
-      bool ok = true;
+      for (int k = 0; k < 2; ++k) {
+        const uint2* row = base + (size_t)min(s0 + k, p.xw - 1) * pitch;
+        h[k] = ld_tagged2_sys(row);
 #pragma unroll
-      for (int e = 0; e < 8; ++e) ok = ok && v[e].y == seq;
-      if (ok) break;
-      __nanosleep(i < 256 ? 100 : 20000);
+        for (int e = 0; e < 4; ++e) v[k][e] = ld_tagged2_sys(row + 2 + 8 * sub + 2 * e);
+      }
+      ok = true;
 #pragma unroll
-      for (int e = 0; e < 8; ++e) v[e] = ld_tagged_sys(row + e);
+      for (int k = 0; k < 2; ++k) {
+        ok = ok && h[k].y == seq && h[k].w == seq;
+#pragma unroll
+        for (int e = 0; e < 4; ++e) ok = ok && v[k][e].y == seq && v[k][e].w == seq;
+      }
     }
+    timed_out = timed_out || !ok;
 #pragma unroll
-    for (int e = 0; e < 8; ++e) timed_out = timed_out || v[e].y != seq;
-    const float wgt = (ms[s] == -INFINITY) ? 0.f : __expf(ms[s] - m_all);
+    for (int k = 0; k < 2; ++k)
+      if (s0 + k < p.xw) {
+        const float mk = __uint_as_float(h[k].x);
+        const float wgt = (mk == -INFINITY) ? 0.f : __expf(mk - m_all);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) acc[e] += wgt * __uint_as_float(v[e].x);
-    l += wgt * ls[s];
+        for (int e = 0; e < 4; ++e) {
+          acc[2 * e] += wgt * __uint_as_float(v[k][e].x);
+          acc[2 * e + 1] += wgt * __uint_as_float(v[k][e].z);
+        }
+        l += wgt * __uint_as_float(h[k].z);
+      }
   }
   if (timed_out) atomicExch(p.err, R2K_ERR_DEVICE_TIMEOUT);
   lsum = l;

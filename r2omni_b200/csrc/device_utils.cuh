@@ -138,6 +138,12 @@ __device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) {
 __device__ __forceinline__ void st_tagged_sys(uint2* p, uint32_t payload, uint32_t tag) {
   asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};\n" ::"l"(p), "r"(payload), "r"(tag) : "memory");
 }
+// Two adjacent tagged words in one 16-byte load (each 8-byte half is still one transaction of its writer).
+__device__ __forceinline__ uint4 ld_tagged2_sys(const uint2* p) {
+  uint4 v;
+  asm volatile("ld.relaxed.sys.global.v4.u32 {%0, %1, %2, %3}, [%4];\n" : "=r"(v.x), "=r"(v.y), "=r"(v.z), "=r"(v.w) : "l"(p) : "memory");
+  return v;
+}
 __device__ __forceinline__ uint2 ld_tagged_sys(const uint2* p) {
   uint2 v;
   asm volatile("ld.relaxed.sys.global.v2.u32 {%0, %1}, [%2];\n" : "=r"(v.x), "=r"(v.y) : "l"(p) : "memory");
