@@ -329,7 +329,7 @@ __device__ __forceinline__ void write_output(const DecodeParams& p, size_t orow,
 
 // Step counter of the fused cross-rank merge: given by the host, or (xseq == 0) kept on the device behind the
 // state words of this rank's exchange buffer, so that a captured graph can be replayed.  Every reader sees the value
-// of the previous step; the CTA that finishes last moves it on at the very end of the kernel.
+// of the previous step; the CTA that counts in last moves it on (exchange_count_in).
 __device__ __forceinline__ uint32_t* exchange_counter(const DecodeParams& p) {
   return reinterpret_cast<uint32_t*>(reinterpret_cast<uint8_t*>(p.xbuf[p.xrank]) + p.xflags_off);
 }
@@ -339,29 +339,52 @@ __device__ __forceinline__ uint32_t exchange_step(const DecodeParams& p) {
   return s == 0 ? 1u : s;
 }
 
+// Hand-over of the device-side step counter: every CTA has read the counter (after the previous launch completed)
+// before it counts in, so the CTA that counts in last may move the counter on for the next launch while this one
+// is still streaming -- nothing of it is left for the end of the kernel.
+__device__ __forceinline__ void exchange_count_in(const DecodeParams& p, uint32_t step) {
+  uint32_t* ctr = exchange_counter(p);
+  if (atomicAdd(ctr + 1, 1u) == (uint32_t)p.grid - 1u) {
+    ctr[1] = 0u;
+    ctr[0] = step;
+  }
+}
+
 // Fused cross-rank merge of one (request, kv head), run by the head's last-arriving CTA on every rank.  Every
-// state value travels as an 8-byte (value, step) word: the 128 worker threads store this rank's rows into every
-// rank's exchange buffer (plain peer stores over NVLink), then poll the words of their own channels in the local
+// state value travels as an 8-byte (value, step) word: the CTA stores this rank's rows into every rank's
+// exchange buffer (plain peer stores over NVLink), then the 128 workers poll the words of their own channels in the local
 // buffer until all carry this step's tag (bounded), and fold the ranks' rows in rank order.  No fence, no
 // separate flag, no barrier.  A buffer holds two halves (step parity) of [world][rows][130] words; the tag makes a
 // stale word of an older step unmistakable.  On return (lsum, acc) hold the merged state; the caller normalises
 // and stores as usual.
 // Not inlined: it runs once per (request, kv head) and must not cost the streaming loop any registers.
-__device__ __noinline__ void exchange_merge(const DecodeParams& p, uint32_t seq, size_t orow, bool valid, bool worker, int sub,
-                                               float mx, float& lsum, float (&acc)[8]) {
-  if (!worker || !valid) return;
+__device__ __noinline__ void exchange_merge(const DecodeParams& p, uint32_t seq, size_t orow, int hh, bool worker, int sub,
+                                               float* staging, float mx, float& lsum, float (&acc)[8]) {
+  const bool valid = hh < p.gqa;
   const uint32_t par = seq & 1u;
   const size_t rows = (size_t)p.g.batch * p.g.num_q_heads;
-  const size_t mine = ((size_t)(par * p.xw + p.xrank) * rows + orow) * 130;
-  for (int r = 0; r < p.xw; ++r) {
-    uint2* o = reinterpret_cast<uint2*>(p.xbuf[r]) + mine;
-    if (sub == 0) {
-      st_tagged_sys(o, __float_as_uint(mx * kLn2), seq);
-      st_tagged_sys(o + 1, __float_as_uint(lsum), seq);
-    }
+  // Send side.  The workers lay this head group's rows out in shared memory as [gqa][130] floats; then all
+  // consumer threads copy them to every rank, consecutive threads writing consecutive 16-byte pairs of tagged
+  // words: a warp's store covers four whole 128-byte lines of the peer's buffer.  (Stores of one thread's own
+  // eight channels would touch sixteen lines per instruction and take several times as long to leave the SM.)
+  if (worker && valid) {
+    float* r = staging + hh * 130;
+    if (sub == 0) *reinterpret_cast<float2*>(r) = make_float2(mx * kLn2, lsum);
 #pragma unroll
-    for (int e = 0; e < 8; ++e) st_tagged_sys(o + 2 + 8 * sub + e, __float_as_uint(acc[e]), seq);
+    for (int e = 0; e < 8; e += 2) *reinterpret_cast<float2*>(r + 2 + 8 * sub + e) = make_float2(acc[e], acc[e + 1]);
   }
+  named_bar_sync(1, kConsumers);
+  {
+    const uint32_t pairs = (uint32_t)p.gqa * 65u;   // 16-byte pairs of tagged words per rank
+    const size_t first = ((size_t)(par * p.xw + p.xrank) * rows + (orow - hh)) * 130;
+    const float2* src = reinterpret_cast<const float2*>(staging);
+    for (uint32_t i = threadIdx.x; i < pairs * (uint32_t)p.xw; i += kConsumers) {
+      const uint32_t r = i / pairs, c = i - r * pairs;
+      const float2 v = src[c];
+      st_tagged2_sys(reinterpret_cast<uint2*>(p.xbuf[r]) + first + 2 * c, __float_as_uint(v.x), __float_as_uint(v.y), seq);
+    }
+  }
+  if (!worker || !valid) return;
   const uint2* base = reinterpret_cast<const uint2*>(p.xbuf[p.xrank]) + ((size_t)(par * p.xw) * rows + orow) * 130;
   const size_t pitch = rows * 130;   // words between two ranks' copies of this row
   float m_all = -INFINITY, l = 0.f;
@@ -579,6 +602,9 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const __gr
   bool alive = true;
   WarpState st;
   grid_dependency_wait();
+  // step tag of the fused cross-rank merge: read once, here, by everybody (see the counter hand-over below)
+  const uint32_t xstep = p.xw > 1 ? exchange_step(p) : 0u;
+  const bool xcount = p.xw > 1 && p.xseq == 0 && threadIdx.x == 0;
 
   for (int bh = bh_lo; bh <= bh_hi; ++bh) {
     const int b = bh / p.g.num_kv_heads, h = bh - b * p.g.num_kv_heads;
@@ -713,6 +739,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const __gr
     if (threadIdx.x == 0) {
       __threadfence();
       const int ticket = atomicAdd(&p.group_counter[bh * p.groups_cap + grp], 1);
+      if (xcount && bh == bh_lo) exchange_count_in(p, xstep);   // in flight together with the ticket
       flags[0] = (ticket == gsize - 1);
       if (flags[0]) p.group_counter[bh * p.groups_cap + grp] = 0;
       __threadfence();
@@ -775,20 +802,12 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const __gr
             __ldg(reinterpret_cast<const uint2*>((const uint8_t*)p.app_v + src));
       }
       const size_t orow = (size_t)b * p.g.num_q_heads + h * p.gqa + hh;
-      if (p.xw > 1) exchange_merge(p, exchange_step(p), orow, hh < p.gqa, worker, sub, mx, lsum, acc);
+      if (p.xw > 1) exchange_merge(p, xstep, orow, hh, worker, sub, scratch, mx, lsum, acc);
       if (worker) write_output<BF16>(p, orow, hh < p.gqa, sub, mx, lsum, acc);
     }
     named_bar_sync(1, kConsumers);  // scratch and flags are reused by the next (request, kv head)
   }
-  if (p.xw > 1 && p.xseq == 0 && threadIdx.x == 0) {
-    uint32_t* ctr = exchange_counter(p);
-    __threadfence();
-    if (atomicAdd(ctr + 1, 1u) == (uint32_t)p.grid - 1u) {   // every CTA is past its last read of the counter
-      const uint32_t next = exchange_step(p);
-      ctr[1] = 0u;
-      ctr[0] = next;
-    }
-  }
+  if (xcount && bh_lo > bh_hi) { __threadfence(); exchange_count_in(p, xstep); }   // a CTA without work counts in too
 }
 
 // ---------------------------------------------------------------------------

@@ -138,6 +138,10 @@ __device__ __forceinline__ void st_relaxed_sys(uint32_t* p, uint32_t v) {
 __device__ __forceinline__ void st_tagged_sys(uint2* p, uint32_t payload, uint32_t tag) {
   asm volatile("st.relaxed.sys.global.v2.u32 [%0], {%1, %2};\n" ::"l"(p), "r"(payload), "r"(tag) : "memory");
 }
+// Two adjacent tagged words in one 16-byte store (same guarantee per 8-byte half).
+__device__ __forceinline__ void st_tagged2_sys(uint2* p, uint32_t a, uint32_t b, uint32_t tag) {
+  asm volatile("st.relaxed.sys.global.v4.u32 [%0], {%1, %2, %3, %2};\n" ::"l"(p), "r"(a), "r"(tag), "r"(b) : "memory");
+}
 // Two adjacent tagged words in one 16-byte load (each 8-byte half is still one transaction of its writer).
 __device__ __forceinline__ uint4 ld_tagged2_sys(const uint2* p) {
   uint4 v;
