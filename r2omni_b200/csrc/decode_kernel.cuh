@@ -352,12 +352,13 @@ __device__ __forceinline__ void exchange_count_in(const DecodeParams& p, uint32_
 
 // Fused cross-rank merge of one (request, kv head), run by the head's last-arriving CTA on every rank.  Every
 // state value travels as an 8-byte (value, step) word: the CTA stores this rank's rows into every rank's
-// exchange buffer (plain peer stores over NVLink), then the 128 workers poll the words of their own channels in the local
-// buffer until all carry this step's tag (bounded), and fold the ranks' rows in rank order.  No fence, no
+// exchange buffer (plain peer stores over NVLink), then polls the ranks' rows in the local buffer until every
+// word carries this step's tag (bounded), and the 128 workers fold the rows in rank order.  No fence, no
 // separate flag, no barrier.  A buffer holds two halves (step parity) of [world][rows][130] words; the tag makes a
 // stale word of an older step unmistakable.  On return (lsum, acc) hold the merged state; the caller normalises
 // and stores as usual.
 // Not inlined: it runs once per (request, kv head) and must not cost the streaming loop any registers.
+static_assert(R2K_MAX_RANKS * 8 * 130 * 4 <= kScratchBytes, "every rank's rows of one head group fit the merge scratch");
 __device__ __noinline__ void exchange_merge(const DecodeParams& p, uint32_t seq, size_t orow, int hh, bool worker, int sub,
                                                float* staging, float mx, float& lsum, float (&acc)[8]) {
   const bool valid = hh < p.gqa;
@@ -378,75 +379,68 @@ __device__ __noinline__ void exchange_merge(const DecodeParams& p, uint32_t seq,
     const uint32_t pairs = (uint32_t)p.gqa * 65u;   // 16-byte pairs of tagged words per rank
     const size_t first = ((size_t)(par * p.xw + p.xrank) * rows + (orow - hh)) * 130;
     const float2* src = reinterpret_cast<const float2*>(staging);
+#pragma unroll 4
     for (uint32_t i = threadIdx.x; i < pairs * (uint32_t)p.xw; i += kConsumers) {
       const uint32_t r = i / pairs, c = i - r * pairs;
       const float2 v = src[c];
       st_tagged2_sys(reinterpret_cast<uint2*>(p.xbuf[r]) + first + 2 * c, __float_as_uint(v.x), __float_as_uint(v.y), seq);
     }
   }
-  if (!worker || !valid) return;
-  const uint2* base = reinterpret_cast<const uint2*>(p.xbuf[p.xrank]) + ((size_t)(par * p.xw) * rows + orow) * 130;
-  const size_t pitch = rows * 130;   // words between two ranks' copies of this row
-  float m_all = -INFINITY, l = 0.f;
-  bool timed_out = false;
-  // pass 1: every rank's maximum -- the reference point needs all of them.  Four ranks' loads are in flight
-  // together: polling rank after rank would pay one memory latency per rank.
+  // Receive side.  All consumer threads bring the ranks' rows of this head group from the local exchange buffer
+  // into shared memory, eight 16-byte loads in flight per thread and poll; a pair counts when both of its words
+  // carry this step's tag.  Polls are bounded (about 1.3 s in all: ranks may be skewed by host work).
+  named_bar_sync(1, kConsumers);   // the send loop has read the staged rows: the space is reused
+  {
+    const uint32_t pairs = (uint32_t)p.gqa * 65u, total = pairs * (uint32_t)p.xw;
+    const uint2* base = reinterpret_cast<const uint2*>(p.xbuf[p.xrank]) + ((size_t)(par * p.xw) * rows + (orow - hh)) * 130;
+    const size_t pitch = rows * 130;   // words between two ranks' copies of a row
+    float2* dst = reinterpret_cast<float2*>(staging);
+    bool timed_out = false;
 #pragma unroll 1
-  for (int s0 = 0; s0 < p.xw; s0 += 4) {
-    uint4 h[4];
-    bool ok = false;
-    for (uint32_t i = 0; i < (1u << 16) && !ok; ++i) {
-      if (i) __nanosleep(i < 256 ? 100 : 20000);   // about 1.3 s in all: ranks may be skewed by host work
+    for (uint32_t i0 = threadIdx.x; i0 < total; i0 += 8 * kConsumers) {
+      uint4 w[8];
+      bool ok = false;
+      for (uint32_t it = 0; it < (1u << 16) && !ok; ++it) {
+        if (it) __nanosleep(it < 256 ? 100 : 20000);
 #pragma unroll
-      for (int k = 0; k < 4; ++k) h[k] = ld_tagged2_sys(base + (size_t)min(s0 + k, p.xw - 1) * pitch);
-      ok = true;
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t i = min(i0 + k * kConsumers, total - 1u), r = i / pairs, c = i - r * pairs;
+          w[k] = ld_tagged2_sys(base + r * pitch + 2 * c);
+        }
+        ok = true;
 #pragma unroll
-      for (int k = 0; k < 4; ++k) ok = ok && h[k].y == seq && h[k].w == seq;
+        for (int k = 0; k < 8; ++k) ok = ok && w[k].y == seq && w[k].w == seq;
+      }
+      timed_out = timed_out || !ok;
+#pragma unroll
+      for (int k = 0; k < 8; ++k) {
+        const uint32_t i = i0 + k * kConsumers;
+        if (i < total) dst[i] = make_float2(__uint_as_float(w[k].x), __uint_as_float(w[k].z));
+      }
     }
-    timed_out = timed_out || !ok;
-#pragma unroll
-    for (int k = 0; k < 4; ++k) m_all = fmaxf(m_all, __uint_as_float(h[k].x));
+    if (timed_out) atomicExch(p.err, R2K_ERR_DEVICE_TIMEOUT);
   }
+  named_bar_sync(1, kConsumers);
+  if (!worker || !valid) return;
+  // fold the ranks' rows in rank order around the common maximum
+  const int rank_floats = p.gqa * 130;
+  const float* mine = staging + hh * 130;
+  float m_all = -INFINITY, l = 0.f;
+  for (int r = 0; r < p.xw; ++r) m_all = fmaxf(m_all, mine[r * rank_floats]);
 #pragma unroll
   for (int e = 0; e < 8; ++e) acc[e] = 0.f;
-  // pass 2: (max, sum) again and this thread's eight channels, two ranks in flight at a time (more would cost
-  // registers), folded in rank order
-#pragma unroll 1
-  for (int s0 = 0; s0 < p.xw; s0 += 2) {
-    uint4 h[2], v[2][4];
-    bool ok = false;
-    for (uint32_t i = 0; i < (1u << 16) && !ok; ++i) {
-      if (i) __nanosleep(i < 256 ? 100 : 20000);
+  for (int r = 0; r < p.xw; ++r) {
+    const float* row = mine + r * rank_floats;
+    const float mk = row[0];
+    const float wgt = (mk == -INFINITY) ? 0.f : __expf(mk - m_all);
 #pragma unroll
-      for (int k = 0; k < 2; ++k) {
-        const uint2* row = base + (size_t)min(s0 + k, p.xw - 1) * pitch;
-        h[k] = ld_tagged2_sys(row);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) v[k][e] = ld_tagged2_sys(row + 2 + 8 * sub + 2 * e);
-      }
-      ok = true;
-#pragma unroll
-      for (int k = 0; k < 2; ++k) {
-        ok = ok && h[k].y == seq && h[k].w == seq;
-#pragma unroll
-        for (int e = 0; e < 4; ++e) ok = ok && v[k][e].y == seq && v[k][e].w == seq;
-      }
+    for (int e = 0; e < 8; e += 2) {
+      const float2 v = *reinterpret_cast<const float2*>(row + 2 + 8 * sub + e);
+      acc[e] += wgt * v.x;
+      acc[e + 1] += wgt * v.y;
     }
-    timed_out = timed_out || !ok;
-#pragma unroll
-    for (int k = 0; k < 2; ++k)
-      if (s0 + k < p.xw) {
-        const float mk = __uint_as_float(h[k].x);
-        const float wgt = (mk == -INFINITY) ? 0.f : __expf(mk - m_all);
-#pragma unroll
-        for (int e = 0; e < 4; ++e) {
-          acc[2 * e] += wgt * __uint_as_float(v[k][e].x);
-          acc[2 * e + 1] += wgt * __uint_as_float(v[k][e].z);
-        }
-        l += wgt * __uint_as_float(h[k].z);
-      }
+    l += wgt * row[1];
   }
-  if (timed_out) atomicExch(p.err, R2K_ERR_DEVICE_TIMEOUT);
   lsum = l;
 }
 
