@@ -217,8 +217,10 @@ class ReplicaBench:
                 i += 1
         return total, steps, flushes
 
-    def run_api_steps(self, steps, host_in, host_out, start=0):
-        """Public operator call with host buffers: H2D of q/k/v, decode+append, D2H of the output."""
+    def run_api_steps(self, steps, host_in, host_out, start=0, torch_copies=False):
+        """Public operator call with host buffers, one call per step (SplitKExecutor.step_host = r2k_decode_host):
+        H2D of q/k/v from pinned memory, decode+append, D2H of the output, wait.  `torch_copies` issues the same
+        step as three torch calls around the device-tensor operator instead (timed beside it for comparison)."""
         total = 0
         nq, nk = self.q.numel(), self.k.numel()
         dev_in = self._dev_in
@@ -230,6 +232,9 @@ class ReplicaBench:
                 self.R.flush_recent(a)
                 a.k_active, a.i2_active = self.base[s]
             total += self.step_bytes(a.recent_len + 1)
+            if not torch_copies:
+                e.step_host(host_in, host_out, append_indices=(self.tokens + i, self.tokens + i))
+                continue
             dev_in.copy_(host_in, non_blocking=True)
             q = dev_in[:nq].view(self.batch, HQ, D)
             k = dev_in[nq : nq + nk].view(self.batch, HKV, D)
@@ -536,7 +541,12 @@ def main():
         e_ms, e_bytes = time_region(device, lambda: bench.run_api_steps(e2e_steps, host_in, host_out, start=warmup), dist_on)
         e2e = {"value": round(e_bytes * world / (e_ms * 1e-3) / 1e9, 1), "unit": "GB/s",
                "us_per_step": round(e_ms * 1e3 / e2e_steps, 2), "steps": e2e_steps,
-               "h2d_bytes_per_step": int(host_in.numel() * 2), "d2h_bytes_per_step": int(host_out.numel() * 2)}
+               "h2d_bytes_per_step": int(host_in.numel() * 2), "d2h_bytes_per_step": int(host_out.numel() * 2),
+               "call": "SplitKExecutor.step_host (r2k_decode_host): pinned H2D copy, decode+append, D2H copy, stream wait"}
+        t_steps = min(e2e_steps, 256)
+        t_ms, _ = time_region(device, lambda: bench.run_api_steps(t_steps, host_in, host_out, start=warmup + e2e_steps,
+                                                                  torch_copies=True), dist_on)
+        e2e["us_per_step_three_torch_calls"] = round(t_ms * 1e3 / t_steps, 2)
     del bench
     torch.cuda.empty_cache()
 

@@ -172,6 +172,26 @@ int r2k_decode(const R2KGeom* geom, const R2KCacheView* view, const void* q, con
 int r2k_decode_static(const R2KGeom* geom, const R2KCacheView* view, const void* q, const R2KAppend* append,
                       void* out, uint32_t flags, void* stream);
 
+/*
+ * r2k_decode for a caller whose query, appended rows and result live in HOST memory: ONE call copies the
+ * inputs to the device, launches the decode (with its fused append), copies the result back and waits for
+ * the stream, so that `host_out` can be read on return.  This is the call a host runtime binds when its
+ * tensors are not device-resident (the reference's operator receives torch CUDA tensors, so there the copies
+ * are the caller's `.to(device)` / `.cpu()` around SplitKExecutor.__call__,
+ * r2omni/sspa/kernels/triton_fourq_splitk.py:1739-1850).
+ *
+ *   host_in  : q [B,Hq,128] of T, followed -- only if append != NULL -- by k [B,Hkv,128] and v [B,Hkv,128]
+ *              of T, contiguous.  Page-locked memory makes the copies asynchronous; pageable memory works.
+ *   append   : NULL, or the indices / scalars of R2KAppend; its k and v pointers are ignored.
+ *   staging  : device scratch of at least r2k_decode_host_staging_bytes() bytes, 16-byte aligned.
+ *   host_out : as `out` of r2k_decode (R2K_FLAG_OUT_* honoured).
+ * Returns the decode's status; a CUDA failure of a copy or of the wait is R2K_ERR_CUDA.
+ */
+int r2k_decode_host_staging_bytes(const R2KGeom* geom, size_t* bytes);
+int r2k_decode_host(const R2KGeom* geom, const R2KCacheView* view, const void* host_in, const R2KAppend* append,
+                    void* workspace, size_t workspace_bytes, void* staging, size_t staging_bytes, void* host_out,
+                    uint32_t flags, void* stream);
+
 /* Copies the device-side status word of the last decodes that used `workspace`
  * into *status (R2K_OK or R2K_ERR_DEVICE_TIMEOUT).  Synchronises `stream`.     */
 int r2k_decode_device_status(void* workspace, int32_t* status, void* stream);

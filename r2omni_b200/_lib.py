@@ -15,6 +15,7 @@ EXPORTS = (
     "r2k_decode_static", "r2k_decode_device_status", "r2k_merge_states", "r2k_pack_k_int4", "r2k_pack_v_int4", "r2k_pack_v_int2",
     "r2k_gather_rows", "r2k_fwht128", "r2k_qk_mrope", "r2k_append_recent", "r2k_flush_recent",
     "r2k_exchange_bytes", "r2k_exchange_create", "r2k_exchange_open", "r2k_exchange_close", "r2k_decode_exchange",
+    "r2k_decode_host_staging_bytes", "r2k_decode_host",
 )
 
 
@@ -68,6 +69,8 @@ def lib():
         handle.r2k_decode.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p,
                                       C.c_uint32, C.c_void_p]
         handle.r2k_decode_exchange.argtypes = handle.r2k_decode.argtypes[:8] + [C.c_void_p, C.c_void_p]
+        handle.r2k_decode_host.argtypes = [C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_void_p, C.c_size_t, C.c_void_p,
+                                           C.c_size_t, C.c_void_p, C.c_uint32, C.c_void_p]
         _lib = handle
     return _lib
 

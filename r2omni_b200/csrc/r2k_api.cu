@@ -369,6 +369,55 @@ int r2k_decode(const R2KGeom* geom, const R2KCacheView* view, const void* q, con
   return decode_impl(geom, view, q, append, workspace, workspace_bytes, out, flags, nullptr, stream);
 }
 
+namespace {
+// q | k | v | out, each rounded up to 256 bytes
+struct HostStaging { size_t q, kv, in_bytes, out_off, out_max, total; };
+bool host_staging(const R2KGeom* g, HostStaging& s) {
+  if (g == nullptr || g->batch < 1 || g->num_q_heads < 1 || g->num_kv_heads < 1) return false;
+  s.q = (size_t)g->batch * g->num_q_heads * 128 * 2;
+  s.kv = (size_t)g->batch * g->num_kv_heads * 128 * 2;
+  s.in_bytes = s.q + 2 * s.kv;
+  s.out_off = (s.in_bytes + 255) & ~(size_t)255;
+  s.out_max = (size_t)g->batch * g->num_q_heads * 130 * 4;
+  s.total = s.out_off + ((s.out_max + 255) & ~(size_t)255);
+  return true;
+}
+}  // namespace
+
+int r2k_decode_host_staging_bytes(const R2KGeom* geom, size_t* bytes) {
+  HostStaging s;
+  if (bytes == nullptr) return R2K_ERR_NULL;
+  if (!host_staging(geom, s)) return R2K_ERR_GEOMETRY;
+  *bytes = s.total;
+  return R2K_OK;
+}
+
+int r2k_decode_host(const R2KGeom* geom, const R2KCacheView* view, const void* host_in, const R2KAppend* append,
+                    void* workspace, size_t workspace_bytes, void* staging, size_t staging_bytes, void* host_out,
+                    uint32_t flags, void* stream) {
+  if (geom == nullptr || host_in == nullptr || host_out == nullptr || staging == nullptr) return R2K_ERR_NULL;
+  HostStaging s;
+  if (!host_staging(geom, s)) return R2K_ERR_GEOMETRY;
+  if (staging_bytes < s.total) return R2K_ERR_WORKSPACE;
+  if (reinterpret_cast<uintptr_t>(staging) & 15u) return R2K_ERR_ALIGNMENT;
+  cudaStream_t st = static_cast<cudaStream_t>(stream);
+  uint8_t* dev = static_cast<uint8_t*>(staging);
+  const size_t rows = (size_t)geom->batch * geom->num_q_heads;
+  const size_t out_bytes = (flags & R2K_FLAG_OUT_STATE) ? rows * 130 * 4 : (flags & R2K_FLAG_OUT_F32) ? rows * 128 * 4 : rows * 128 * 2;
+  if (cudaMemcpyAsync(dev, host_in, append ? s.in_bytes : s.q, cudaMemcpyHostToDevice, st) != cudaSuccess) return R2K_ERR_CUDA;
+  R2KAppend dev_append;
+  if (append != nullptr) {
+    dev_append = *append;
+    dev_append.k = dev + s.q;
+    dev_append.v = dev + s.q + s.kv;
+  }
+  const int status = decode_impl(geom, view, dev, append ? &dev_append : nullptr, workspace, workspace_bytes, dev + s.out_off,
+                                 flags, nullptr, stream);
+  if (status != R2K_OK) return status;
+  if (cudaMemcpyAsync(host_out, dev + s.out_off, out_bytes, cudaMemcpyDeviceToHost, st) != cudaSuccess) return R2K_ERR_CUDA;
+  return cudaStreamSynchronize(st) == cudaSuccess ? R2K_OK : R2K_ERR_CUDA;
+}
+
 int r2k_decode_exchange(const R2KGeom* geom, const R2KCacheView* view, const void* q, const R2KAppend* append, void* workspace,
                         size_t workspace_bytes, void* out, uint32_t flags, const R2KExchange* exchange, void* stream) {
   if (exchange == nullptr) return R2K_ERR_NULL;

@@ -121,6 +121,7 @@ class SplitKExecutor:
         self._view_obj, self._view_ref = None, None
         self._ws_ptr, self._ws_size = workspace.buffer.data_ptr(), workspace.buffer.numel()
         self._qshape = (arenas.batch, self.num_query_heads, 128)
+        self._host_staging = None
 
     @property
     def batched(self) -> bool:
@@ -193,6 +194,50 @@ class SplitKExecutor:
         if append is not None and self.batched:
             a.recent_len += 1
         return ws.output
+
+    def step_host(self, host_in: torch.Tensor, host_out: torch.Tensor, append_indices=None) -> torch.Tensor:
+        """One decode step for a caller whose tensors live in host memory (r2k_decode_host): ``host_in`` is the
+        query [B,Hq,128] followed, when ``append_indices = (global_index, logical_position)`` (two ints) is given,
+        by the new key and value rows [B,Hkv,128] each, in one contiguous CPU tensor of the cache's element type
+        (pinned for asynchronous copies); the result is written to ``host_out`` [B,Hq,128] (same type) and can be
+        read on return: the call copies in, launches the decode with its fused append, copies out and waits."""
+        a = self.arenas
+        if a.dtype != torch.bfloat16:
+            raise ValueError("step_host supports bf16 caches")
+        nq, nkv = a.batch * self.num_query_heads * 128, a.batch * a.num_kv_heads * 128
+        need = nq + (2 * nkv if append_indices is not None else 0)
+        if (host_in.device.type != "cpu" or host_out.device.type != "cpu" or host_in.dtype != a.dtype
+                or host_out.dtype != a.dtype or not host_in.is_contiguous() or not host_out.is_contiguous()
+                or host_in.numel() < need or host_out.numel() != nq):
+            raise ValueError("host buffers do not match the prepared split-K executor")
+        if append_indices is None and a.n_fp + a.n_i4 + a.i2_active + a.recent_len == 0:
+            raise ValueError("four-quadrant cache has no surviving tokens")
+        ap = None
+        if append_indices is not None:
+            if a.recent_len >= a.recent_capacity:
+                raise RuntimeError("prepared executor cannot fuse an append into a full Recent-FP pool")
+            ap = self._append
+            ap.k, ap.v, ap.indices = None, None, None
+            ap.global_index, ap.logical_position = int(append_indices[0]), int(append_indices[1])
+            ap = self._append_ref
+        if self._host_staging is None:
+            n = C.c_size_t()
+            L.check(self._lib.r2k_decode_host_staging_bytes(self._geom_ref, C.byref(n)), "r2k_decode_host_staging_bytes")
+            self._host_staging = torch.empty(n.value, device=a.device, dtype=torch.uint8)
+        geom = self._geom
+        geom.n_i2 = a.i2_active
+        view = a.view()
+        if view is not self._view_obj:
+            self._view_obj, self._view_ref = view, C.byref(view)
+        flags = L.FLAG_OUTPUT_HADAMARD if self.output_hadamard else 0
+        status = self._lib.r2k_decode_host(self._geom_ref, self._view_ref, host_in.data_ptr(), ap, self._ws_ptr, self._ws_size,
+                                           self._host_staging.data_ptr(), self._host_staging.numel(), host_out.data_ptr(),
+                                           flags, _stream_ptr(a.device))
+        if status:
+            L.check(status, "r2k_decode_host")
+        if append_indices is not None and self.batched:
+            a.recent_len += 1
+        return host_out
 
     def decode_f32(self, query: torch.Tensor, append=None) -> torch.Tensor:
         """Same launch with an un-rounded float32 result (parity checks)."""

@@ -217,3 +217,42 @@ def test_operator_argument_errors():
         R.prepare_splitk_executor(object(), ex.workspace)
     with pytest.raises(ValueError):
         R.build_three_precision_cache(queries[0][0].cuda(), queries[0][0].cuda(), None, cache_variant="v_fourq_k_bf16")
+
+
+def test_host_buffer_step_matches_device_call_and_oracle():
+    """r2k_decode_host (SplitKExecutor.step_host): pinned host query / new rows in, host result out, one call per
+    step.  Same bits as the device-tensor call on a twin cache, same ring afterwards, oracle parity."""
+    classes = seeded_classes(24, 5)
+    hq, hkv, s = 16, 2, 24 * 64
+    twins = [both_caches(77, hq=hq, hkv=hkv, tokens=s, page=64, classes=classes, appends=6, n_queries=6) for _ in range(2)]
+    ocache, new_k, new_v, queries = twins[0][0], twins[0][2], twins[0][3], twins[0][4]
+    ex_dev, ex_host = make_executor(twins[0][1], hq), make_executor(twins[1][1], hq)
+    host_in = torch.empty(hq * 128 + 2 * hkv * 128, dtype=torch.bfloat16).pin_memory()
+    host_out = torch.empty(1, hq, 128, dtype=torch.bfloat16).pin_memory()
+    for i in range(6):
+        q = queries[i].reshape(1, hq, 128)
+        host_in[: hq * 128] = q.flatten()
+        host_in[hq * 128 : hq * 128 + hkv * 128] = new_k[i].flatten()
+        host_in[hq * 128 + hkv * 128 :] = new_v[i].flatten()
+        want = ex_dev(q.cuda(), append=(new_k[i].unsqueeze(0).contiguous().cuda(), new_v[i].unsqueeze(0).contiguous().cuda(),
+                                        s + i, s + i)).cpu()
+        got = ex_host.step_host(host_in, host_out, append_indices=(s + i, s + i))
+        assert torch.equal(got.view(torch.int16), want.view(torch.int16)), f"step {i}"
+        O.append_token(ocache, new_k[i], new_v[i], s + i, s + i)
+        assert_close(got.float(), O.decode_fp32(q.float(), ocache), f"host step {i}")
+    # without an append: the query alone travels
+    want = ex_dev(queries[0].reshape(1, hq, 128).cuda()).cpu()
+    host_in[: hq * 128] = queries[0].flatten()
+    got = ex_host.step_host(host_in, host_out)
+    assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    a_dev, a_host = twins[0][1].arenas, twins[1][1].arenas   # the ring after six fused appends: device state of the twins
+    for name in ("recent_k", "recent_v", "recent_len_device", "recent_global", "recent_logical", "recent_page_lengths"):
+        assert torch.equal(getattr(a_dev, name), getattr(a_host, name)), name
+    assert int(a_host.recent_len_device[0]) == ocache.recent_len == 6
+    assert torch.equal(a_host.recent_k[0][:, :6].cpu().view(torch.int16), ocache.recent_k[:, :6].view(torch.int16))
+    assert torch.equal(a_host.recent_v[0][:, :6].cpu().view(torch.int16), ocache.recent_v[:, :6].view(torch.int16))
+    assert ex_host.device_status() == 0
+    with pytest.raises(ValueError):
+        ex_host.step_host(host_in[: hq * 128], host_out, append_indices=(0, 0))   # rows missing
+    with pytest.raises(ValueError):
+        ex_host.step_host(host_in.cuda(), host_out)
