@@ -370,6 +370,7 @@ int r2k_decode(const R2KGeom* geom, const R2KCacheView* view, const void* q, con
 }
 
 namespace {
+constexpr int kHostZeroCopyDefault = 2;   // result written in place: measured faster; inputs copied: measured faster
 // q | k | v | out, each rounded up to 256 bytes
 struct HostStaging { size_t q, kv, in_bytes, out_off, out_max, total; };
 bool host_staging(const R2KGeom* g, HostStaging& s) {
@@ -404,17 +405,34 @@ int r2k_decode_host(const R2KGeom* geom, const R2KCacheView* view, const void* h
   uint8_t* dev = static_cast<uint8_t*>(staging);
   const size_t rows = (size_t)geom->batch * geom->num_q_heads;
   const size_t out_bytes = (flags & R2K_FLAG_OUT_STATE) ? rows * 130 * 4 : (flags & R2K_FLAG_OUT_F32) ? rows * 128 * 4 : rows * 128 * 2;
-  if (cudaMemcpyAsync(dev, host_in, append ? s.in_bytes : s.q, cudaMemcpyHostToDevice, st) != cudaSuccess) return R2K_ERR_CUDA;
+  // Page-locked, device-mapped host buffers can be used by the kernel in place (its accesses to q, the new rows
+  // and the result are plain loads and stores): bit 0 of R2K_HOST_ZERO_COPY lets it read host_in over PCIe, bit 1
+  // lets it write host_out; a buffer that is not mapped (or pageable) takes the copy.
+  static const int zero_copy = [] { const char* e = getenv("R2K_HOST_ZERO_COPY"); return e ? atoi(e) : kHostZeroCopyDefault; }();
+  auto mapped = [](const void* p) -> uint8_t* {
+    cudaPointerAttributes a;
+    if (cudaPointerGetAttributes(&a, p) != cudaSuccess) { cudaGetLastError(); return nullptr; }
+    return a.type == cudaMemoryTypeHost ? static_cast<uint8_t*>(a.devicePointer) : nullptr;
+  };
+  uint8_t* in = (zero_copy & 1) ? mapped(host_in) : nullptr;
+  uint8_t* out = (zero_copy & 2) ? mapped(host_out) : nullptr;
+  if (in != nullptr && (reinterpret_cast<uintptr_t>(in) & 15u)) in = nullptr;
+  if (out != nullptr && (reinterpret_cast<uintptr_t>(out) & 15u)) out = nullptr;
+  if (in == nullptr) {
+    if (cudaMemcpyAsync(dev, host_in, append ? s.in_bytes : s.q, cudaMemcpyHostToDevice, st) != cudaSuccess) return R2K_ERR_CUDA;
+    in = dev;
+  }
   R2KAppend dev_append;
   if (append != nullptr) {
     dev_append = *append;
-    dev_append.k = dev + s.q;
-    dev_append.v = dev + s.q + s.kv;
+    dev_append.k = in + s.q;
+    dev_append.v = in + s.q + s.kv;
   }
-  const int status = decode_impl(geom, view, dev, append ? &dev_append : nullptr, workspace, workspace_bytes, dev + s.out_off,
-                                 flags, nullptr, stream);
+  const int status = decode_impl(geom, view, in, append ? &dev_append : nullptr, workspace, workspace_bytes,
+                                 out ? out : dev + s.out_off, flags, nullptr, stream);
   if (status != R2K_OK) return status;
-  if (cudaMemcpyAsync(host_out, dev + s.out_off, out_bytes, cudaMemcpyDeviceToHost, st) != cudaSuccess) return R2K_ERR_CUDA;
+  if (out == nullptr && cudaMemcpyAsync(host_out, dev + s.out_off, out_bytes, cudaMemcpyDeviceToHost, st) != cudaSuccess)
+    return R2K_ERR_CUDA;
   return cudaStreamSynchronize(st) == cudaSuccess ? R2K_OK : R2K_ERR_CUDA;
 }
 
