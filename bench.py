@@ -542,7 +542,7 @@ def main():
         e2e = {"value": round(e_bytes * world / (e_ms * 1e-3) / 1e9, 1), "unit": "GB/s",
                "us_per_step": round(e_ms * 1e3 / e2e_steps, 2), "steps": e2e_steps,
                "h2d_bytes_per_step": int(host_in.numel() * 2), "d2h_bytes_per_step": int(host_out.numel() * 2),
-               "call": "SplitKExecutor.step_host (r2k_decode_host): pinned H2D copy, decode+append writing the pinned result over PCIe, stream wait"}
+               "call": "SplitKExecutor.step_host (r2k_decode_host): H2D copy kernel from the pinned block, decode+append writing the pinned result over PCIe, stream wait"}
         t_steps = min(e2e_steps, 256)
         t_ms, _ = time_region(device, lambda: bench.run_api_steps(t_steps, host_in, host_out, start=warmup + e2e_steps,
                                                                   torch_copies=True), dist_on)

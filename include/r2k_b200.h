@@ -186,7 +186,8 @@ int r2k_decode_static(const R2KGeom* geom, const R2KCacheView* view, const void*
  *   staging  : device scratch of at least r2k_decode_host_staging_bytes() bytes, 16-byte aligned.
  *   host_out : as `out` of r2k_decode (R2K_FLAG_OUT_* honoured).
  * A page-locked, device-mapped `host_out` is written by the kernel in place (no copy back); environment variable
- * R2K_HOST_ZERO_COPY selects otherwise (bit 0: read `host_in` in place, bit 1: write `host_out` in place; default 2).
+ * R2K_HOST_ZERO_COPY selects otherwise (bit 0: read `host_in` in place, bit 1: write `host_out` in place, bit 2:
+ * bring a mapped `host_in` into `staging` with a copy kernel that the decode launch overlaps; default 6).
  * Returns the decode's status; a CUDA failure of a copy or of the wait is R2K_ERR_CUDA.
  */
 int r2k_decode_host_staging_bytes(const R2KGeom* geom, size_t* bytes);

@@ -7,6 +7,8 @@
 #include <cuda_fp16.h>
 #include <stdint.h>
 
+#include "device_utils.cuh"
+
 namespace r2k {
 
 template <bool BF16>
@@ -176,6 +178,16 @@ __global__ void __launch_bounds__(128) gather_rows_kernel(const uint16_t* src, i
   const int64_t s = index ? index[i] : i;
   const uint2 w = *reinterpret_cast<const uint2*>(src + ((int64_t)head * src_rows + s) * 128 + 4 * lane);
   *reinterpret_cast<uint2*>(dst + ((int64_t)head * dst_rows + dst_start + i) * 128 + 4 * lane) = w;
+}
+
+// ---- host block copy ---------------------------------------------------------
+// Brings a block of page-locked, device-mapped host memory into device memory with plain loads over PCIe, 16 bytes
+// per thread.  A decode launched behind it with programmatic stream serialization runs its prologue and starts
+// streaming the packed pools meanwhile; it reads the block only after this grid has completed.
+__global__ void __launch_bounds__(256) host_block_copy_kernel(const uint4* __restrict__ src, uint4* __restrict__ dst, int n16) {
+  launch_dependents();
+  const int i = blockIdx.x * 256 + threadIdx.x;
+  if (i < n16) dst[i] = src[i];
 }
 
 // ---- residual ring ----------------------------------------------------------
