@@ -107,8 +107,8 @@ class ClockSampler:
 
 
 # dram__bytes_read.sum + dram__bytes_write.sum of one decode_kernel launch on the default workload, from the ncu
-# capture summarised in profiles/decode_kernel_b8_32k.md (96.55 MB read + 4.32 MB written, mean of two launches).
-NCU_DRAM_BYTES_PER_LAUNCH = 100_870_000
+# capture summarised in profiles/decode_kernel_b8_32k.md (96.55 MB read + 3.09 MB written, mean of two launches).
+NCU_DRAM_BYTES_PER_LAUNCH = 99_630_000
 
 
 def measured_peak_gbs():
