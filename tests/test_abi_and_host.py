@@ -86,6 +86,22 @@ def test_exchange_entry_points_validate_without_a_gpu(lib):
     assert lib.r2k_exchange_close(None, 0) == L.OK
 
 
+def test_host_buffer_entry_points_validate_without_a_gpu(lib):
+    g = L.Geom()
+    g.batch, g.num_q_heads, g.num_kv_heads, g.head_dim, g.dtype = 8, 16, 2, 128, L.DTYPE_BF16
+    need = C.c_size_t(0)
+    assert lib.r2k_decode_host_staging_bytes(C.byref(g), C.byref(need)) == L.OK
+    inputs = 8 * 16 * 128 * 2 + 2 * 8 * 2 * 128 * 2            # q | k | v
+    result = 8 * 16 * 130 * 4                                    # the largest output form (state rows)
+    assert need.value == (inputs + 255) // 256 * 256 + (result + 255) // 256 * 256
+    assert lib.r2k_decode_host_staging_bytes(C.byref(g), None) == L.ERR_NULL
+    assert lib.r2k_decode_host_staging_bytes(None, C.byref(need)) == L.ERR_GEOMETRY
+    buf = (C.c_uint8 * 64)()
+    assert lib.r2k_decode_host(C.byref(g), None, None, None, None, 0, None, 0, None, 0, None) == L.ERR_NULL
+    # staging too small: refused before any CUDA call
+    assert lib.r2k_decode_host(C.byref(g), None, buf, None, None, 0, buf, 64, buf, 0, None) == L.ERR_WORKSPACE
+
+
 def test_missing_library_is_a_loud_error(monkeypatch):
     monkeypatch.setattr(L, "_lib", None)
     monkeypatch.setattr(L, "LIB", "/nonexistent/libr2k_b200.so")
