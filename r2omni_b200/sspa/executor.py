@@ -116,6 +116,7 @@ class SplitKExecutor:
         self._idx = None
         # per-step constants of the launch, built once
         self._decode = self._lib.r2k_decode
+        self._decode_host = self._lib.r2k_decode_host
         self._geom_ref = C.byref(self._geom)
         self._append_ref = C.byref(self._append)
         self._view_obj, self._view_ref = None, None
@@ -214,7 +215,7 @@ class SplitKExecutor:
                 or host_in.numel() < need or host_out.numel() != nq):
             raise ValueError("host buffers do not match the prepared split-K executor")
         else:
-            self._host_pair = (host_in, host_out, need)
+            self._host_pair = (host_in, host_out, need, host_in.data_ptr(), host_out.data_ptr())
         if append_indices is None and a.n_fp + a.n_i4 + a.i2_active + a.recent_len == 0:
             raise ValueError("four-quadrant cache has no surviving tokens")
         ap = None
@@ -229,15 +230,16 @@ class SplitKExecutor:
             n = C.c_size_t()
             L.check(self._lib.r2k_decode_host_staging_bytes(self._geom_ref, C.byref(n)), "r2k_decode_host_staging_bytes")
             self._host_staging = torch.empty(n.value, device=a.device, dtype=torch.uint8)
+            self._host_staging_ptr, self._host_staging_size = self._host_staging.data_ptr(), n.value
         geom = self._geom
         geom.n_i2 = a.i2_active
         view = a.view()
         if view is not self._view_obj:
             self._view_obj, self._view_ref = view, C.byref(view)
         flags = L.FLAG_OUTPUT_HADAMARD if self.output_hadamard else 0
-        status = self._lib.r2k_decode_host(self._geom_ref, self._view_ref, host_in.data_ptr(), ap, self._ws_ptr, self._ws_size,
-                                           self._host_staging.data_ptr(), self._host_staging.numel(), host_out.data_ptr(),
-                                           flags, _stream_ptr(a.device))
+        pair = self._host_pair
+        status = self._decode_host(self._geom_ref, self._view_ref, pair[3], ap, self._ws_ptr, self._ws_size,
+                                   self._host_staging_ptr, self._host_staging_size, pair[4], flags, _stream_ptr(a.device))
         if status:
             L.check(status, "r2k_decode_host")
         if append_indices is not None and self.batched:
