@@ -56,24 +56,31 @@ __global__ void __launch_bounds__(64) pack_k_int4_kernel(PackArgs a, uint8_t* pa
   const float old_s0 = __half2float(srow[2 * c]), old_s1 = __half2float(srow[2 * c + 1]);
   const float old_z0 = (float)zrow[2 * c], old_z1 = (float)zrow[2 * c + 1];
 
-  auto fetch = [&](int64_t r, float& x0, float& x1) {
+  // The block's values (raw 16-bit pairs: re-quantised rows are element-rounded, so nothing is lost) are staged in
+  // shared memory by the first pass: its loads are independent and run several at a time, and the second pass
+  // reads no global memory, so its stores do not wait behind loads that might alias them.
+  extern __shared__ uint32_t staged_words[];   // k_block rows of 64 words (dynamic: k_block * 256 bytes)
+  uint32_t (*staged)[64] = reinterpret_cast<uint32_t (*)[64]>(staged_words);
+  auto fetch_raw = [&](int64_t r) -> uint32_t {
     if (r < a.dst_start) {
       const uint8_t byte = prow[r * 64 + c];
-      x0 = round_through_elem<BF16>(__fmul_rn(__fsub_rn((float)(byte & 15), old_z0), old_s0));
-      x1 = round_through_elem<BF16>(__fmul_rn(__fsub_rn((float)(byte >> 4), old_z1), old_s1));
-    } else {
-      const int64_t i = r - a.dst_start;
-      const int64_t s = a.index ? a.index[i] : i;
-      const uint32_t w = *reinterpret_cast<const uint32_t*>(src + s * 128 + 2 * c);
-      x0 = raw_to_float<BF16>((uint16_t)(w & 0xffffu));
-      x1 = raw_to_float<BF16>((uint16_t)(w >> 16));
+      const float x0 = __fmul_rn(__fsub_rn((float)(byte & 15), old_z0), old_s0);
+      const float x1 = __fmul_rn(__fsub_rn((float)(byte >> 4), old_z1), old_s1);
+      if (BF16) return (uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(x0)) | ((uint32_t)__bfloat16_as_ushort(__float2bfloat16_rn(x1)) << 16);
+      return (uint32_t)__half_as_ushort(__float2half_rn(x0)) | ((uint32_t)__half_as_ushort(__float2half_rn(x1)) << 16);
     }
+    const int64_t i = r - a.dst_start;
+    const int64_t s = a.index ? a.index[i] : i;
+    return *reinterpret_cast<const uint32_t*>(src + s * 128 + 2 * c);
   };
 
   float lo0 = INFINITY, hi0 = -INFINITY, lo1 = INFINITY, hi1 = -INFINITY;
-  for (int64_t r = r_begin; r < r_end; ++r) {
-    float x0, x1;
-    fetch(r, x0, x1);
+  const int rows = (int)(r_end - r_begin);
+#pragma unroll 8
+  for (int i = 0; i < rows; ++i) {
+    const uint32_t w = fetch_raw(r_begin + i);
+    staged[i][c] = w;
+    const float x0 = raw_to_float<BF16>((uint16_t)(w & 0xffffu)), x1 = raw_to_float<BF16>((uint16_t)(w >> 16));
     lo0 = fminf(lo0, x0); hi0 = fmaxf(hi0, x0);
     lo1 = fminf(lo1, x1); hi1 = fmaxf(hi1, x1);
   }
@@ -83,12 +90,13 @@ __global__ void __launch_bounds__(64) pack_k_int4_kernel(PackArgs a, uint8_t* pa
   const float st1 = fmaxf(__fdiv_rn(__fsub_rn(hi1, lo1), 15.f), 1.0e-6f);
   const float zp0 = fminf(fmaxf(rintf(__fdiv_rn(-lo0, st0)), 0.f), 15.f);
   const float zp1 = fminf(fmaxf(rintf(__fdiv_rn(-lo1, st1)), 0.f), 15.f);
-  for (int64_t r = r_begin; r < r_end; ++r) {
-    float x0, x1;
-    fetch(r, x0, x1);  // reads the old byte of this very location before it is overwritten below
+#pragma unroll 4
+  for (int i = 0; i < rows; ++i) {
+    const uint32_t w = staged[i][c];   // written by this very thread
+    const float x0 = raw_to_float<BF16>((uint16_t)(w & 0xffffu)), x1 = raw_to_float<BF16>((uint16_t)(w >> 16));
     const float q0 = fminf(fmaxf(rintf(__fadd_rn(__fdiv_rn(x0, st0), zp0)), 0.f), 15.f);
     const float q1 = fminf(fmaxf(rintf(__fadd_rn(__fdiv_rn(x1, st1), zp1)), 0.f), 15.f);
-    prow[r * 64 + c] = (uint8_t)((uint32_t)q0 | ((uint32_t)q1 << 4));
+    prow[(r_begin + i) * 64 + c] = (uint8_t)((uint32_t)q0 | ((uint32_t)q1 << 4));
   }
   srow[2 * c] = __float2half_rn(st0);
   srow[2 * c + 1] = __float2half_rn(st1);

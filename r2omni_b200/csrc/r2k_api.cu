@@ -188,7 +188,7 @@ int launch_pack_k(const PackArgs& a, int batch, uint8_t* packed, void* scale, ui
                   int k_block, cudaStream_t st) {
   const int64_t first = a.dst_start / k_block, last = (a.dst_start + a.count - 1) / k_block;
   dim3 grid((unsigned)(last - first + 1), (unsigned)a.num_heads, (unsigned)batch);
-  pack_k_int4_kernel<BF16><<<grid, 64, 0, st>>>(a, packed, reinterpret_cast<__half*>(scale), zero, pb, sb, zb, k_block, first);
+  pack_k_int4_kernel<BF16><<<grid, 64, (size_t)k_block * 256, st>>>(a, packed, reinterpret_cast<__half*>(scale), zero, pb, sb, zb, k_block, first);
   ++g_launches;
   return cudaGetLastError() == cudaSuccess ? R2K_OK : R2K_ERR_CUDA;
 }
