@@ -125,8 +125,10 @@ typedef struct R2KAppend {
  * (r2omni/sspa/kernels/triton_fourq_splitk.py:1607-1692). */
 int r2k_decode_workspace_bytes(const R2KGeom* geom, size_t* bytes);
 
-/* Clears the arrival counters at the head of a workspace.  Call once after
- * allocating it (and after any decode that reported a device timeout).        */
+/* Clears the status word and the arrival counters at the head of a workspace.
+ * Call once after allocating it (and after any decode that reported a device
+ * timeout).  One workspace may serve launches of different geometries one after
+ * another on a stream, as long as it is large enough for each of them.          */
 int r2k_decode_workspace_init(void* workspace, size_t bytes, void* stream);
 
 /*
@@ -163,14 +165,22 @@ int r2k_decode(const R2KGeom* geom, const R2KCacheView* view, const void* q, con
  *  - The first call on each device resolves the array's device address (cudaGetSymbolAddress, with
  *    that device current) and clears its counters; make that first call outside any stream capture.
  *  - Every call on a device shares the one array, which keeps the previous call's contents.  The
- *    kernel re-zeroes the counters it used, so back-to-back calls on ONE stream are fine; calls that
- *    may overlap on the GPU (different streams, or graphs replayed concurrently) race on it and must
- *    be serialised by the caller, or use r2k_decode with separate workspaces.
+ *    arrival counters live in a block of fixed size and position and every launch leaves the ones it
+ *    used at zero, so back-to-back calls on ONE stream are fine, also when their geometries differ;
+ *    calls that may overlap on the GPU (different streams, or graphs replayed concurrently) race on it
+ *    and must be serialised by the caller, or use r2k_decode with separate workspaces.
  *  - Inputs, outputs, flags and results are exactly those of r2k_decode.
+ *  - r2k_decode_static_status reads the device-side status word of the static scratch (what
+ *    r2k_decode_device_status is for a caller-provided workspace; it synchronises `stream`), and
+ *    r2k_decode_static_reset clears that word and the arrival counters on `stream` (what
+ *    r2k_decode_workspace_init is for a workspace: call it after a reported device timeout).  Neither
+ *    allocates; either may be the first call on a device.
  */
 #define R2K_STATIC_WORKSPACE_BYTES (4u << 20)
 int r2k_decode_static(const R2KGeom* geom, const R2KCacheView* view, const void* q, const R2KAppend* append,
                       void* out, uint32_t flags, void* stream);
+int r2k_decode_static_status(int32_t* status, void* stream);
+int r2k_decode_static_reset(void* stream);
 
 /*
  * r2k_decode for a caller whose query, appended rows and result live in HOST memory: ONE call copies the
@@ -232,15 +242,19 @@ int r2k_merge_states(const float* states, int32_t num_states, int64_t state_stri
  * which is what a captured CUDA graph needs; two steps in flight
  * never share a buffer half because a rank cannot finish step n+1 before every
  * rank has finished step n).  A rank that is missing makes the others give up
- * after a bounded wait (about a second) and report R2K_ERR_DEVICE_TIMEOUT through
- * r2k_decode_device_status; nothing hangs.
+ * after a bounded wait (about a second, see wait_us) and report
+ * R2K_ERR_DEVICE_TIMEOUT through r2k_decode_device_status; nothing hangs.  Rows
+ * that never arrived count as the state of a rank without tokens, so `out` then
+ * holds the finite merge of the ranks that did arrive.
  */
 #define R2K_MAX_RANKS 8
 typedef struct R2KExchange {
   void*    buffers[R2K_MAX_RANKS]; /* rank r's exchange buffer as mapped in this process */
   int32_t  rank, world;
   uint32_t seq;                    /* step counter 1, 2, 3, ... or 0: use the counter kept in the buffer */
-  uint32_t reserved;
+  uint32_t wait_us;                /* budget, in microseconds, of the wait for the other ranks' rows before it
+                                      gives up (65536 polls share it; a poll itself takes about a microsecond, so
+                                      the shortest wait is some 70 ms); 0 selects the default, about 1.3 s   */
 } R2KExchange;
 
 /* Bytes of one rank's exchange buffer for this geometry and world size. */

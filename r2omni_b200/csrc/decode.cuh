@@ -47,6 +47,13 @@ constexpr int kSmemBytes = kStages * kStageBytes + kScratchBytes + 256;
 // both levels cost one dependent round trip to memory for up to kMergeGroup * kMergeGroup CTAs per head.
 constexpr int kMergeGroup = 9;
 constexpr int kWsHeaderBytes = 256;
+// The arrival counters sit in a block of fixed size behind the header, so that the partial slots start at the
+// same offset for every geometry whose counters fit: launches of different geometries may then share one
+// workspace (each launch leaves the counters it used at zero, and no launch writes floats where another expects
+// a counter).  Only a geometry with more counters than this gets a larger block.
+constexpr size_t kWsCounterBlockBytes = 64u << 10;
+constexpr uint32_t kExchangePolls = 1u << 16;     // polls of the cross-rank wait before it gives up
+constexpr uint32_t kExchangeNapNs = 20000;        // default sleep between polls: about 1.3 s in all
 
 struct DecodeParams {
   R2KGeom g;
@@ -81,6 +88,7 @@ struct DecodeParams {
   // counter at byte offset xflags_off.
   int xw, xrank;
   uint32_t xseq, xflags_off;
+  uint32_t xnap;                  // nanoseconds the cross-rank wait sleeps between two polls
   float* xbuf[R2K_MAX_RANKS];
   alignas(64) CUtensorMap fp_map;
 };

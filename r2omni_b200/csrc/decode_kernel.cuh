@@ -388,7 +388,8 @@ __device__ __noinline__ void exchange_merge(const DecodeParams& p, uint32_t seq,
   }
   // Receive side.  All consumer threads bring the ranks' rows of this head group from the local exchange buffer
   // into shared memory, eight 16-byte loads in flight per thread and poll; a pair counts when both of its words
-  // carry this step's tag.  Polls are bounded (about 1.3 s in all: ranks may be skewed by host work).
+  // carry this step's tag.  Polls are bounded: kExchangePolls rounds with p.xnap nanoseconds of sleep between them (about
+  // 1.3 s by default: ranks may be skewed by host work).
   named_bar_sync(1, kConsumers);   // the send loop has read the staged rows: the space is reused
   {
     const uint32_t pairs = (uint32_t)p.gqa * 65u, total = pairs * (uint32_t)p.xw;
@@ -396,12 +397,13 @@ __device__ __noinline__ void exchange_merge(const DecodeParams& p, uint32_t seq,
     const size_t pitch = rows * 130;   // words between two ranks' copies of a row
     float2* dst = reinterpret_cast<float2*>(staging);
     bool timed_out = false;
+    const uint32_t nap = p.xnap;   // nanoseconds between two polls once the first 256 quick ones are spent
 #pragma unroll 1
     for (uint32_t i0 = threadIdx.x; i0 < total; i0 += 8 * kConsumers) {
       uint4 w[8];
       bool ok = false;
-      for (uint32_t it = 0; it < (1u << 16) && !ok; ++it) {
-        if (it) __nanosleep(it < 256 ? 100 : 20000);
+      for (uint32_t it = 0; it < kExchangePolls && !ok; ++it) {
+        if (it) __nanosleep(it < 256 ? 100 : nap);
 #pragma unroll
         for (int k = 0; k < 8; ++k) {
           const uint32_t i = min(i0 + k * kConsumers, total - 1u), r = i / pairs, c = i - r * pairs;
@@ -416,6 +418,19 @@ __device__ __noinline__ void exchange_merge(const DecodeParams& p, uint32_t seq,
       for (int k = 0; k < 8; ++k) {
         const uint32_t i = i0 + k * kConsumers;
         if (i < total) dst[i] = make_float2(__uint_as_float(w[k].x), __uint_as_float(w[k].z));
+      }
+      if (!ok) {
+        // A pair that never arrived (the wait ran out) is taken as the state of a rank without tokens:
+        // (max, sum) = (-inf, 0), values 0.  The output then is the merge of the ranks that did arrive: finite.
+#pragma unroll 1
+        for (int k = 0; k < 8; ++k) {
+          const uint32_t i = i0 + k * kConsumers;
+          if (i >= total) break;
+          const uint32_t r = i / pairs, c = i - r * pairs;
+          const uint4 v = ld_tagged2_sys(base + r * pitch + 2 * c);
+          if (v.y != seq || v.w != seq) dst[i] = (c % 65u == 0u) ? make_float2(-INFINITY, 0.f) : make_float2(0.f, 0.f);
+          else dst[i] = make_float2(__uint_as_float(v.x), __uint_as_float(v.z));
+        }
       }
     }
     if (timed_out) atomicExch(p.err, R2K_ERR_DEVICE_TIMEOUT);

@@ -16,24 +16,44 @@ std::atomic<uint64_t> g_launches{0};
 
 struct DeviceInfo {
   int sms = 0;
-  bool attr_set = false;
+  bool ready = false;
   bool pdl = true;   // R2K_DISABLE_PDL=1 in the environment turns programmatic dependent launch off (debugging)
 };
 DeviceInfo g_dev[64];
+std::mutex g_dev_mutex;
 
+// Per-device facts and the kernels' function attributes, set up once per device under a lock: the first calls of
+// two host threads may race here.
 int device_info(DeviceInfo** out) {
   int dev = 0;
   if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return R2K_ERR_CUDA;
   DeviceInfo& d = g_dev[dev];
-  if (d.sms == 0) {
+  std::lock_guard<std::mutex> lock(g_dev_mutex);
+  if (!d.ready) {
     int sms = 0;
     if (cudaDeviceGetAttribute(&sms, cudaDevAttrMultiProcessorCount, dev) != cudaSuccess || sms <= 0) return R2K_ERR_CUDA;
+    if (cudaFuncSetAttribute(decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess ||
+        cudaFuncSetAttribute(decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
+      return R2K_ERR_CUDA;
+    cudaFuncSetAttribute(decode_kernel<true>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
+    cudaFuncSetAttribute(decode_kernel<false>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
     d.sms = sms;
     const char* off = std::getenv("R2K_DISABLE_PDL");
     d.pdl = !(off != nullptr && off[0] == '1');
+    d.ready = true;
   }
   *out = &d;
   return R2K_OK;
+}
+
+// R2K_GRID_CAP=<n> in the environment (read at every call, so a test can change it inside one process) limits
+// the decode grid to n CTAs: small caches then put many tiles on one CTA, which is how the tests reach the
+// pipeline's stage reuse, phase flips and head crossings without benchmark-sized inputs.
+int grid_cap_from_env() {
+  const char* cap = std::getenv("R2K_GRID_CAP");
+  if (cap == nullptr || cap[0] == 0) return 0;
+  const int v = std::atoi(cap);
+  return v > 0 ? v : 0;
 }
 
 inline bool pow2_in(int v, int a, int b, int c) { return v == a || v == b || v == c; }
@@ -100,7 +120,9 @@ int derive(const R2KGeom* g, DecodeParams* p) {
   }
   p->cF = w[0]; p->c4 = w[1]; p->c2 = w[2]; p->cR = w[3];
   const int64_t total_units = (int64_t)p->units * p->bh_total;
-  const int64_t cap = (int64_t)dev->sms * kCtasPerSm;
+  int64_t cap = (int64_t)dev->sms * kCtasPerSm;
+  const int env_cap = grid_cap_from_env();
+  if (env_cap > 0 && env_cap < cap) cap = env_cap;
   p->grid = (int)(total_units < cap ? total_units : cap);
   // a whole number of CTAs per (request, kv head) when there is room: no CTA pays the partial/merge protocol twice
   if (p->grid >= 2 * p->bh_total) p->grid = p->grid / p->bh_total * p->bh_total;
@@ -116,8 +138,8 @@ int derive(const R2KGeom* g, DecodeParams* p) {
 }
 
 size_t counters_bytes(const DecodeParams& p) {
-  const size_t n = (size_t)(p.bh_total + p.g.batch + p.bh_total * p.groups_cap) * sizeof(int);
-  return (n + 255) / 256 * 256;
+  const size_t n = ((size_t)(p.bh_total + p.g.batch + p.bh_total * p.groups_cap) * sizeof(int) + 255) / 256 * 256;
+  return n < kWsCounterBlockBytes ? kWsCounterBlockBytes : n;
 }
 size_t workspace_need(const DecodeParams& p) {
   return kWsHeaderBytes + counters_bytes(p) +
@@ -330,20 +352,18 @@ static int decode_impl(const R2KGeom* geom, const R2KCacheView* view, const void
       p.xbuf[r] = reinterpret_cast<float*>(ex->buffers[r]);
     }
     p.xw = ex->world; p.xrank = ex->rank; p.xseq = ex->seq;
+    // wait budget -> sleep between polls (the number of polls is fixed); a poll itself takes about a microsecond
+    p.xnap = kExchangeNapNs;
+    if (ex->wait_us != 0) {
+      const uint64_t nap = (uint64_t)ex->wait_us * 1000u / kExchangePolls;
+      p.xnap = nap > 1000000u ? 1000000u : (uint32_t)nap;
+    }
     p.xflags_off = (uint32_t)exchange_states_bytes(geom, ex->world);
   }
 
   DeviceInfo* dev;
   rc = device_info(&dev);
   if (rc) return rc;
-  if (!dev->attr_set) {
-    if (cudaFuncSetAttribute(decode_kernel<true>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess ||
-        cudaFuncSetAttribute(decode_kernel<false>, cudaFuncAttributeMaxDynamicSharedMemorySize, kSmemBytes) != cudaSuccess)
-      return R2K_ERR_CUDA;
-    cudaFuncSetAttribute(decode_kernel<true>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-    cudaFuncSetAttribute(decode_kernel<false>, cudaFuncAttributePreferredSharedMemoryCarveout, cudaSharedmemCarveoutMaxShared);
-    dev->attr_set = true;
-  }
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   // Programmatic stream serialization: when the previous kernel of the stream signals early (a decode launch
   // does), this grid's CTAs may start on free SMs and prefetch pool tiles; the kernel itself waits for the
@@ -504,6 +524,23 @@ static __device__ __align__(256) unsigned char g_static_workspace[R2K_STATIC_WOR
 namespace {
 std::mutex g_static_mutex;
 void* g_static_ptr[64] = {};
+constexpr size_t kStaticHeadBytes = kWsHeaderBytes + kWsCounterBlockBytes;   // status word + arrival counters
+
+// Device address of the static scratch on the current device.  The first call on a device resolves it
+// (cudaGetSymbolAddress with that device current) and clears the status word and the counters on `stream`.
+int static_workspace(void** out, cudaStream_t stream) {
+  int dev = 0;
+  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return R2K_ERR_CUDA;
+  std::lock_guard<std::mutex> lock(g_static_mutex);
+  if (g_static_ptr[dev] == nullptr) {
+    void* p = nullptr;
+    if (cudaGetSymbolAddress(&p, g_static_workspace) != cudaSuccess || p == nullptr) return R2K_ERR_CUDA;
+    if (cudaMemsetAsync(p, 0, kStaticHeadBytes, stream) != cudaSuccess) return R2K_ERR_CUDA;
+    g_static_ptr[dev] = p;
+  }
+  *out = g_static_ptr[dev];
+  return R2K_OK;
+}
 }  // namespace
 
 extern "C" {
@@ -514,22 +551,24 @@ int r2k_decode_static(const R2KGeom* geom, const R2KCacheView* view, const void*
   int rc = r2k_decode_workspace_bytes(geom, &need);
   if (rc) return rc;
   if (need > (size_t)R2K_STATIC_WORKSPACE_BYTES) return R2K_ERR_WORKSPACE;
-  int dev = 0;
-  if (cudaGetDevice(&dev) != cudaSuccess || dev < 0 || dev >= 64) return R2K_ERR_CUDA;
   void* ptr = nullptr;
-  {
-    std::lock_guard<std::mutex> lock(g_static_mutex);
-    if (g_static_ptr[dev] == nullptr) {
-      // first call on this device (which is current): resolve the device address of the array and clear the
-      // header and counters at its head; partial slots need no clearing (written before they are read)
-      void* p = nullptr;
-      if (cudaGetSymbolAddress(&p, g_static_workspace) != cudaSuccess || p == nullptr) return R2K_ERR_CUDA;
-      if (cudaMemsetAsync(p, 0, 1u << 16, reinterpret_cast<cudaStream_t>(stream)) != cudaSuccess) return R2K_ERR_CUDA;
-      g_static_ptr[dev] = p;
-    }
-    ptr = g_static_ptr[dev];
-  }
+  rc = static_workspace(&ptr, reinterpret_cast<cudaStream_t>(stream));
+  if (rc) return rc;
   return r2k_decode(geom, view, q, append, ptr, (size_t)R2K_STATIC_WORKSPACE_BYTES, out, flags, stream);
+}
+
+int r2k_decode_static_status(int32_t* status, void* stream) {
+  void* ptr = nullptr;
+  const int rc = static_workspace(&ptr, reinterpret_cast<cudaStream_t>(stream));
+  if (rc) return rc;
+  return r2k_decode_device_status(ptr, status, stream);
+}
+
+int r2k_decode_static_reset(void* stream) {
+  void* ptr = nullptr;
+  const int rc = static_workspace(&ptr, reinterpret_cast<cudaStream_t>(stream));
+  if (rc) return rc;
+  return cudaMemsetAsync(ptr, 0, kStaticHeadBytes, reinterpret_cast<cudaStream_t>(stream)) == cudaSuccess ? R2K_OK : R2K_ERR_CUDA;
 }
 
 int r2k_decode_device_status(void* workspace, int32_t* status, void* stream) {

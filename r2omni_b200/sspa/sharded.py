@@ -12,8 +12,9 @@ window and the flush live on the last rank only.
 
 ``fused=True`` replaces the all-gather and the merge launch by peer stores inside
 the decode kernel: every rank's last CTA of a (request, kv head) writes its state
-rows into every rank's exchange buffer over NVLink, raises a step flag, waits
-(bounded) for the others' flags and merges in place (``r2k_decode_exchange``).
+rows into every rank's exchange buffer over NVLink as (value, step) words, waits
+(bounded) until every rank's words of the step have landed in its own buffer and
+merges in place (``r2k_decode_exchange``).
 """
 from __future__ import annotations
 
@@ -51,7 +52,8 @@ class SequenceShardedExecutor:
     make the same call.
     """
 
-    def __init__(self, local: SplitKExecutor, group=None, *, fused: bool = False, device_step_counter: bool = False):
+    def __init__(self, local: SplitKExecutor, group=None, *, fused: bool = False, device_step_counter: bool = False,
+                 wait_us: int = 0):
         import torch.distributed as dist
         self._dist = dist
         self.local, self.group = local, group
@@ -61,6 +63,9 @@ class SequenceShardedExecutor:
         # the step counter of the fused merge lives on the host (one integer per call) or, for calls that are
         # captured into a CUDA graph and replayed, on the device
         self.device_step_counter = bool(device_step_counter)
+        # microseconds the fused merge waits for the other ranks' rows before it reports a device timeout (0: the
+        # library's default, about a second)
+        self.wait_us = int(wait_us)
         self._exchange, self._mapped, self._own = None, [], None
         if self.fused:
             self._open_exchange()
@@ -87,7 +92,7 @@ class SequenceShardedExecutor:
             handles = [None] * self.world
             self._dist.all_gather_object(handles, (self.rank, bytes(handle)), group=self.group)
             ex = L.Exchange()
-            ex.rank, ex.world, ex.seq = self.rank, self.world, 0
+            ex.rank, ex.world, ex.seq, ex.wait_us = self.rank, self.world, 0, self.wait_us
             for r, raw in handles:
                 if r == self.rank:
                     ex.buffers[r] = own.value

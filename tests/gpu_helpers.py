@@ -9,6 +9,18 @@ from golden_cases import snapshot_arrays
 
 ATOL, RTOL = 2e-3, 1e-2   # attention tolerance of the packed-KV path: max-abs 2e-3 / rel 1e-2
 
+# Decode-grid limits for small inputs (environment variable R2K_GRID_CAP, read by the library at every call):
+# one CTA per (request, kv head) streams every tile of every pool through the shared-memory ring; two CTAs per
+# head add the cross-CTA merge; three CTAs in all make a CTA cross from one head into the next.
+GRID_CAPS = (None, "heads", "2x_heads", "3")
+
+
+def apply_grid_cap(monkeypatch, mode, heads: int) -> None:
+    if mode is None:
+        monkeypatch.delenv("R2K_GRID_CAP", raising=False)
+    else:
+        monkeypatch.setenv("R2K_GRID_CAP", str({"heads": heads, "2x_heads": 2 * heads, "3": 3}[mode]))
+
 
 def make_plan(classes: torch.Tensor, page: int, recent_capacity: int) -> R.LayerCompressionPlan:
     n = int(classes.numel())

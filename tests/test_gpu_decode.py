@@ -7,7 +7,7 @@ import torch
 
 import r2omni_b200 as R
 from r2omni_b200 import _lib as L
-from gpu_helpers import assert_close, build_gpu_cache, image, make_executor
+from gpu_helpers import GRID_CAPS, apply_grid_cap, assert_close, build_gpu_cache, image, make_executor
 from oracle import sspa_oracle as O
 from recipe import make_inputs
 
@@ -71,8 +71,11 @@ def test_int4_only_4096_tokens_with_full_residual_window():
 
 
 @pytest.mark.parametrize("hq,hkv", [(16, 2), (28, 4)])
-def test_mixed_pools_fused_append_every_step(hq, hkv):
-    """Mixed bf16/INT4/INT2 pages (25/50/25), one fused append per decode step across a flush."""
+@pytest.mark.parametrize("grid_cap", GRID_CAPS)
+def test_mixed_pools_fused_append_every_step(hq, hkv, grid_cap, monkeypatch):
+    """Mixed bf16/INT4/INT2 pages (25/50/25), one fused append per decode step across a flush; with a grid limit
+    a CTA streams up to 30 tiles of three pools through the three-stage ring and carries its softmax state across."""
+    apply_grid_cap(monkeypatch, grid_cap, hkv)
     classes = seeded_classes(96, 3)
     ocache, gcache, new_k, new_v, queries = both_caches(22 + hq, hq=hq, hkv=hkv, tokens=96 * 64, page=64, classes=classes,
                                                         appends=140, n_queries=140, append_capacity=256)
@@ -100,8 +103,10 @@ def test_mixed_pools_fused_append_every_step(hq, hkv):
     assert ex.device_status() == 0
 
 
-def test_stacked_batch_matches_per_request_oracle():
+@pytest.mark.parametrize("grid_cap", (None, "heads", "3"))
+def test_stacked_batch_matches_per_request_oracle(grid_cap, monkeypatch):
     """Homogeneous batch (B=3): stacked arenas, per-request oracle; fused append and a batched flush."""
+    apply_grid_cap(monkeypatch, grid_cap, 6)
     classes = seeded_classes(40, 8)
     hq, hkv, s = 16, 2, 40 * 64
     oc, ex1, ks, vs, qs = [], [], [], [], []

@@ -7,7 +7,7 @@ import torch
 
 import r2omni_b200 as R
 from golden_cases import CASES, GoldenCase, compare_snapshot
-from gpu_helpers import assert_close, build_gpu_cache, image, make_executor
+from gpu_helpers import GRID_CAPS, apply_grid_cap, assert_close, build_gpu_cache, image, make_executor
 
 pytestmark = pytest.mark.gpu
 
@@ -19,8 +19,10 @@ def _kwargs(case):
 
 @pytest.mark.parametrize("name", CASES)
 @pytest.mark.parametrize("fused", [False, True])
-def test_fixture_pack_append_flush_and_decode(name, fused):
+@pytest.mark.parametrize("grid_cap", GRID_CAPS)
+def test_fixture_pack_append_flush_and_decode(name, fused, grid_cap, monkeypatch):
     case = GoldenCase(name)
+    apply_grid_cap(monkeypatch, grid_cap, case.hkv)
     cache = build_gpu_cache(case.key, case.value, case.classes, **_kwargs(case))
     compare_snapshot(case, "s0_", image(cache, "s0_"), skip=("recent_k", "recent_v"))
     ex = make_executor(cache, case.hq)

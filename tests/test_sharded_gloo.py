@@ -68,3 +68,40 @@ def test_sharded_decode_protocol_on_cpu_ranks(world, tokens):
     mp.spawn(_worker, args=(world, port, tokens, results), nprocs=world, join=True)
     assert len(results) == world
     assert max(results.values()) < 2e-6, dict(results)
+
+
+def _worker_with_absent_rank(rank, world, port, results):
+    """The last rank joins the group and then never contributes its state.  The others must come back from the
+    exchange step with an error inside the group's (short) timeout and report it; nobody waits for ever."""
+    import datetime
+    import time
+    os.environ.update(MASTER_ADDR="127.0.0.1", MASTER_PORT=str(port))
+    dist.init_process_group("gloo", rank=rank, world_size=world, timeout=datetime.timedelta(seconds=5))
+    t0 = time.monotonic()
+    try:
+        if rank == world - 1:
+            results[rank] = "absent"
+            time.sleep(1.0)          # alive, between steps, but silent
+            return
+        state = torch.zeros(1, 16, 130)
+        gathered = torch.empty(world, 16, 130)
+        try:
+            dist.all_gather_into_tensor(gathered, state)
+            results[rank] = "completed"
+        except Exception:   # noqa: BLE001 -- gloo reports a timeout or a closed connection, depending on timing
+            results[rank] = f"exchange failed after {time.monotonic() - t0:.1f} s"
+    finally:
+        try:
+            dist.destroy_process_group()
+        except Exception:   # noqa: BLE001 -- the group is already broken on the survivors
+            pass
+
+
+def test_a_rank_that_never_contributes_is_reported_not_waited_for():
+    port = _free_port()
+    manager = mp.Manager()
+    results = manager.dict()
+    mp.spawn(_worker_with_absent_rank, args=(3, port, results), nprocs=3, join=True)
+    assert results[2] == "absent"
+    for rank in (0, 1):
+        assert results[rank].startswith("exchange failed"), dict(results)

@@ -7,7 +7,7 @@ no workspace.  This test calls it through the C ABI twice in a row on the same s
 finds the first call's leftovers in the shared array) and checks both results against r2k_decode with a
 caller-provided workspace, within the attention tolerance of the other GPU tests (max-abs 2e-3 + rel 1e-2;
 in practice the two are the same kernel and agree bit for bit).  It also checks that an oversized
-geometry is refused.  The file sorts last so that a failure here cannot hide another test's result.
+geometry is refused, that two geometries can take turns on the array, and the status / reset calls.  The file sorts last so that a failure here cannot hide another test's result.
 """
 import ctypes as C
 
@@ -78,3 +78,40 @@ def test_static_scratch_decode_rejects_oversized_geometry():
     status = L.lib().r2k_decode_static(C.byref(g), C.byref(view), C.c_void_p(dummy.data_ptr()), None,
                                        C.c_void_p(dummy.data_ptr()), C.c_uint32(0), None)
     assert status == L.ERR_WORKSPACE
+
+
+def test_static_scratch_serves_alternating_geometries_and_reports_its_status():
+    """Two geometries whose counters and partial slots would sit at different offsets take turns on the one static
+    array (one request with 2 kv heads, then a stacked batch of 8 requests with 8 kv heads): every result must
+    equal the workspace variant's.  The status word of the static scratch is readable and clearable without the
+    caller ever seeing its address."""
+    import r2omni_b200 as R
+    from r2omni_b200 import _lib as L
+    from r2omni_b200.sspa.cache import _stream_ptr
+    from gpu_helpers import build_gpu_cache, make_executor
+    from recipe import make_inputs
+
+    classes = torch.tensor([2, 5, 1, 2, 5, 2, 1, 5])
+    key, value, _, _, queries = make_inputs(seed=71, hq=16, hkv=2, tokens=512, appends=1, n_queries=2)
+    small = make_executor(build_gpu_cache(key, value, classes, page_size=64), 16)
+    singles = []
+    for b in range(8):
+        k8, v8, _, _, q8 = make_inputs(seed=72 + b, hq=16, hkv=8, tokens=512, appends=1, n_queries=2)
+        singles.append(make_executor(build_gpu_cache(k8, v8, classes, page_size=64), 16))
+    wide = R.stack_homogeneous_splitk_executors(singles)
+    q_wide = torch.randn(2, 8, 16, 128, generator=torch.Generator().manual_seed(3)).to(torch.bfloat16).cuda()
+    stream = C.c_void_p(_stream_ptr(small.arenas.device))
+    assert L.lib().r2k_decode_static_reset(stream) == L.OK
+    for turn in range(2):
+        for ex, q in ((small, queries[turn].cuda()), (wide, q_wide[turn])):
+            want = ex.decode_f32(q).clone()
+            status, got = _static_decode(ex, q)
+            assert status == L.OK, L.lib().r2k_status_string(status)
+            torch.cuda.synchronize()
+            assert torch.equal(got, want), f"turn {turn}, batch {ex.arenas.batch}"
+    word = C.c_int32(-1)
+    assert L.lib().r2k_decode_static_status(C.byref(word), stream) == L.OK and word.value == 0
+    assert L.lib().r2k_decode_static_reset(stream) == L.OK
+    status, got = _static_decode(small, queries[0].cuda())
+    torch.cuda.synchronize()
+    assert status == L.OK and torch.equal(got, small.decode_f32(queries[0].cuda()))
