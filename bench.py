@@ -1,29 +1,35 @@
 #!/usr/bin/env python
 """Benchmark of the SSPA packed-KV decode path on B200.
 
-    python bench.py --gpus N --steps K --warmup W [--impl reference]
+    python bench.py --gpus N --steps K --warmup W [--impl reference] [--workload NAME]
 
-Workload "decode_32k_b8" (default): one layer, 16 query / 2 KV heads of 128 dims,
-batch 8, 32768 cached tokens per request in 64-token pages whose value precision is
-drawn from a seed as bf16 25 % / INT4 50 % / INT2 25 %, INT4 keys in 32-token
-blocks, a 128-token bf16 residual window.  A step is one decode launch over the
-whole batch that also appends one new token per request; every 128 steps the
-residual window is quantized and packed (flush).  Four distinct cache sets are
-visited round-robin (4 x ~98 MB > L2), so every step reads from HBM.
+Workloads (``config.workload``):
 
-``value`` is the whole-job algorithmic GB/s with inputs resident in HBM
-(CUDA-graph replays, device-timed); ``e2e`` is the same metric through the public
-operator call with host query/key/value buffers and a host read of the output
-inside the timed region.  With N > 1 every rank runs its own replica (requests
-are independent: no data-path collective) and the line also carries the
-sequence-sharded 1M-token decode, which does exchange (max, sum-exp, out) states.
+* ``decode_32k_b8`` (default): one layer, 16 query / 2 KV heads of 128 dims, batch 8, 32768 cached tokens per
+  request in 64-token pages whose value precision is drawn from a seed as bf16 25 % / INT4 50 % / INT2 25 %, INT4
+  keys in 32-token blocks, a 128-token bf16 residual window.  A step is one decode launch over the whole batch that
+  also appends one new token per request; every 128 steps the residual window is quantized and packed (flush).
+  Four distinct cache sets are visited round-robin (4 x ~98 MB > L2), so every step reads from HBM.
+* ``decode_4k_b1``: batch 1, 4096 INT4-value tokens in 32-token pages plus a full 128-token residual window; a step
+  is one decode launch (launch-bound: 1.3 MB).  128 cache sets are visited round-robin (168 MB > L2).
+* ``decode_7b_28l``: 28 layers of the 28-query / 4-KV-head shape, batch 16, 65536 tokens per request, mixed pages as
+  above (~21.8 GB resident).  A step is the attention of ALL layers: 28 decode launches with fused append, joined by
+  programmatic dependent launch; every 128 steps all layers flush.
+
+``value`` is the whole-job algorithmic GB/s with inputs resident in HBM (CUDA-graph replays, device-timed); ``e2e``
+is the same metric through the public operator call with host query/key/value buffers and a host read of the output
+inside the timed region.  After the timed regions one decode of the benchmarked caches is compared with the CPU
+oracle (``parity``).  With N > 1 every rank runs its own replica (requests are independent: no data-path collective)
+and the line also carries the sequence-sharded 1M-token decode, which does exchange (max, sum-exp, out) states and
+is checked against the oracle's per-shard states at every N.  ``triton_reference`` times the reference's own Triton
+decoder on the same GPU and the same seeded workload when the reference is installed under ``baseline/_ref``.
 """
 from __future__ import annotations
 
 import argparse
 import json
 import os
-import subprocess
+import statistics
 import sys
 import threading
 import time
@@ -38,6 +44,15 @@ import torch  # noqa: E402
 HQ, HKV, D = 16, 2, 128
 PAGE, K_BLOCK, V2_GROUP, RING = 64, 32, 32, 128
 METRIC = "packed_kv_decode_effective_hbm_gbps"
+ATOL, RTOL = 2e-3, 1e-2   # attention tolerance: max-abs 2e-3 + rel 1e-2
+
+WORKLOADS = {
+    # name: heads, batch, tokens, cache sets, page, (bf16, INT4) page fractions, what a step is, append per step
+    "decode_32k_b8": dict(hq=16, hkv=2, batch=8, tokens=32768, sets=4, page=64, mix=(0.25, 0.5), step="launch", append=True),
+    "decode_4k_b1": dict(hq=16, hkv=2, batch=1, tokens=4096, sets=128, page=32, mix=(0.0, 1.0), step="launch", append=False),
+    "decode_7b_28l": dict(hq=28, hkv=4, batch=16, tokens=65536, sets=28, page=64, mix=(0.25, 0.5), step="round", append=True),
+    "small": dict(hq=16, hkv=2, batch=2, tokens=4096, sets=4, page=64, mix=(0.25, 0.5), step="launch", append=True),
+}
 
 
 def page_classes(n_pages: int, seed: int, p_fp: float, p_i4: float) -> torch.Tensor:
@@ -106,8 +121,8 @@ class ClockSampler:
         return out
 
 
-# dram__bytes_read.sum + dram__bytes_write.sum of one decode_kernel launch on the default workload, from the ncu
-# capture summarised in profiles/decode_kernel_b8_32k.md (96.55 MB read + 3.09 MB written, mean of two launches).
+# dram__bytes_read.sum + dram__bytes_write.sum of one decode_kernel launch on the default workload, taken from an
+# ncu capture of this command (96.55 MB read + 3.09 MB written, mean of two launches); a constant, not measured here.
 NCU_DRAM_BYTES_PER_LAUNCH = 99_630_000
 
 
@@ -119,21 +134,83 @@ def measured_peak_gbs():
     return 6650.0, "fallback"
 
 
+def spread(samples) -> dict:
+    """min / median / max of repeated measurements (so that an outlier can be told from a regression)."""
+    s = sorted(samples)
+    return {"repeats": len(s), "min": round(s[0], 2), "median": round(statistics.median(s), 2), "max": round(s[-1], 2)}
+
+
+def tolerance_excess(got: torch.Tensor, want: torch.Tensor):
+    """(max-abs error, worst excess over atol + rtol*|want|): the result passes when the excess is <= 0."""
+    got, want = got.float().cpu(), want.float().cpu()
+    err = (got - want).abs()
+    return float(err.max()), float((err - (ATOL + RTOL * want.abs())).max())
+
+
+# --------------------------------------------------------------------------- #
+# the unmodified reference, when it is installed beside the repository
+# --------------------------------------------------------------------------- #
+_REFERENCE = None
+
+
+def load_reference():
+    """Modules of the reference package installed in baseline/_ref (oracle/install_reference.py), or the reason why
+    they cannot be used.  Nothing of the product goes through them: they are the baseline being measured."""
+    global _REFERENCE
+    if _REFERENCE is not None:
+        return _REFERENCE
+    path = os.path.join(ROOT, "baseline", "_ref")
+    if not os.path.isdir(os.path.join(path, "r2omni")):
+        _REFERENCE = (None, "the reference is not installed under baseline/_ref")
+        return _REFERENCE
+    if path not in sys.path:
+        sys.path.insert(0, path)
+    sys.dont_write_bytecode = True
+    try:
+        import types
+        ns = types.SimpleNamespace()
+        from r2omni.sspa.kernels.triton_fourq_attention import triton_mixed_reference
+        from r2omni.sspa.runtime.cache_plan import LayerCompressionPlan
+        from r2omni.sspa.runtime.dynamic_fourq_cache import DynamicCacheStats, append_generated_token
+        from r2omni.sspa.runtime.precision_pool import build_three_precision_cache
+        ns.triton_mixed_reference, ns.LayerCompressionPlan = triton_mixed_reference, LayerCompressionPlan
+        ns.DynamicCacheStats, ns.append_generated_token = DynamicCacheStats, append_generated_token
+        ns.build_three_precision_cache = build_three_precision_cache
+        _REFERENCE = (ns, None)
+    except Exception as exc:  # noqa: BLE001 -- reported in the JSON line
+        _REFERENCE = (None, f"the reference under baseline/_ref does not import: {exc!r}"[:300])
+    return _REFERENCE
+
+
+def reference_plan(ns, classes: torch.Tensor, page: int, recent_capacity: int, device="cpu"):
+    """The reference's plan type; its index tensors live where the key/value tensors do."""
+    n = int(classes.numel())
+    pos = torch.arange(n * page, device=device)
+    classes = classes.to(device)
+    sel = lambda c: (classes == c).nonzero().flatten()  # noqa: E731
+    return ns.LayerCompressionPlan(
+        layer_id=0, fp_pages=sel(1), int4_pages=sel(2), int2_pages=sel(5), evicted_pages=sel(0),
+        protected_pages=torch.empty(0, dtype=torch.long, device=device), recent_fp_capacity=recent_capacity,
+        logical_positions=pos, global_token_indices=pos.clone(),
+        page_offsets=torch.arange(n, device=device) * page, page_lengths=torch.full((n,), page, device=device),
+        page_classes=classes)
+
+
 # --------------------------------------------------------------------------- #
 # this library
 # --------------------------------------------------------------------------- #
-def build_batched_executor(batch, tokens, seed, device, p_fp=0.25, p_i4=0.5):
+def build_batched_executor(batch, tokens, seed, device, p_fp=0.25, p_i4=0.5, hq=HQ, hkv=HKV, page=PAGE):
     import r2omni_b200 as R
     from gpu_helpers import make_plan
 
     singles = []
-    classes = page_classes(tokens // PAGE, seed, p_fp, p_i4)
+    classes = page_classes(tokens // page, seed, p_fp, p_i4)
     for b in range(batch):
-        key, value = synth_kv(tokens, seed * 1000 + b, device)
-        cache = R.build_three_precision_cache(key, value, make_plan(classes, PAGE, RING), page_size=PAGE,
+        key, value = synth_kv(tokens, seed * 1000 + b, device, hkv=hkv)
+        cache = R.build_three_precision_cache(key, value, make_plan(classes, page, RING), page_size=page,
                                               key_quantization_superblock=K_BLOCK, int2_group_size=V2_GROUP,
                                               compact_key_append_capacity=RING, recent_flush_size=RING)
-        ws = R.allocate_splitk_workspace(cache, num_query_heads=HQ)
+        ws = R.allocate_splitk_workspace(cache, num_query_heads=hq)
         singles.append(R.prepare_splitk_executor(cache, ws))
         del key, value
     if batch == 1:
@@ -144,115 +221,216 @@ def build_batched_executor(batch, tokens, seed, device, p_fp=0.25, p_i4=0.5):
 
 
 class ReplicaBench:
-    """Round-robin over `sets` batched caches; decode+append every step, flush every 128 steps per set."""
+    """`sets` batched caches visited in order.  A "visit" is one decode launch on one set (with a fused one-token
+    append when the workload appends); a step is one visit, or -- for a multi-layer workload -- one visit of every
+    set.  When a set's residual window is full it is flushed before its next visit."""
 
-    def __init__(self, device, batch=8, tokens=32768, sets=4, p_fp=0.25, p_i4=0.5):
+    def __init__(self, device, *, hq=HQ, hkv=HKV, batch=8, tokens=32768, sets=4, page=PAGE, mix=(0.25, 0.5),
+                 step="launch", append=True, seed0=11):
         import r2omni_b200 as R
         self.R, self.device, self.batch, self.tokens = R, device, batch, tokens
-        self.ex = [build_batched_executor(batch, tokens, 11 + s, device, p_fp, p_i4) for s in range(sets)]
+        self.hq, self.hkv, self.page, self.mix, self.seed0 = hq, hkv, page, mix, seed0
+        self.append, self.visits_per_step = append, (sets if step == "round" else 1)
+        self.ex = [build_batched_executor(batch, tokens, seed0 + s, device, mix[0], mix[1], hq, hkv, page) for s in range(sets)]
         g = torch.Generator(device=device).manual_seed(5)
-        self.q = torch.randn(batch, HQ, D, generator=g, device=device).to(torch.bfloat16)
-        self.k = torch.randn(batch, HKV, D, generator=g, device=device).to(torch.bfloat16)
-        self.v = torch.randn(batch, HKV, D, generator=g, device=device).to(torch.bfloat16)
+        self.q = torch.randn(batch, hq, D, generator=g, device=device).to(torch.bfloat16)
+        self.k = torch.randn(batch, hkv, D, generator=g, device=device).to(torch.bfloat16)
+        self.v = torch.randn(batch, hkv, D, generator=g, device=device).to(torch.bfloat16)
         self.stats = R.DynamicCacheStats()
         self.base = [(e.arenas.k_active, e.arenas.i2_active) for e in self.ex]
         self.step_graphs, self.flush_graphs = [], []
-        # prefill the rings half way so that flushes fall inside short runs too
+        # appending workloads start with the windows half full, so that flushes fall inside short runs too; the
+        # static workload decodes against a full window
         for e in self.ex:
-            for i in range(RING // 2):
-                e(self.q, append=(self.k, self.v, tokens + i, tokens + i))
+            for i in range(RING // 2 if append else RING):
+                if append:
+                    e(self.q, append=(self.k, self.v, tokens + i, tokens + i))
+                    if batch == 1:
+                        e.arenas.recent_len += 1     # a single-request caller advances the host mirror itself
+                else:
+                    R.append_generated_token(e.arenas, self.k if batch > 1 else self.k[0].unsqueeze(1),
+                                             self.v if batch > 1 else self.v[0].unsqueeze(1),
+                                             global_token_index=tokens + i, logical_position=tokens + i, stats=self.stats)
         torch.cuda.synchronize(device)
         for e in self.ex:
             gs, gf = torch.cuda.CUDAGraph(), torch.cuda.CUDAGraph()
             ring = e.arenas.recent_len
             with torch.cuda.graph(gs):
-                e(self.q, append=(self.k, self.v, tokens, tokens))
+                self._visit(e)
             e.arenas.recent_len = ring                     # capture does not run the kernel
-            with torch.cuda.graph(gf):
-                e.arenas.recent_len = RING
-                R.flush_recent(e.arenas)
-            # flushed tokens overwrite the same arena rows on every replay: the context stays at `tokens` + ring
-            e.arenas.k_active, e.arenas.i2_active = self.base[len(self.step_graphs)]
-            e.arenas.recent_len = ring
+            if append:
+                with torch.cuda.graph(gf):
+                    e.arenas.recent_len = RING
+                    R.flush_recent(e.arenas)
+                # flushed tokens overwrite the same arena rows on every replay: the context stays at `tokens` + ring
+                e.arenas.k_active, e.arenas.i2_active = self.base[len(self.step_graphs)]
+                e.arenas.recent_len = ring
             self.step_graphs.append(gs)
-            self.flush_graphs.append(gf)
-        # one graph per round (a step on every set, back to back): consecutive decode launches are joined by
-        # programmatic dependent launch edges, as consecutive layers of a model are
+            self.flush_graphs.append(gf if append else None)
+        # one graph per round (a visit of every set, back to back): consecutive decode launches are joined by
+        # programmatic dependent launch edges, as consecutive layers of a model are.  Large rounds are split into
+        # graphs of at most 32 launches.
         rings = [e.arenas.recent_len for e in self.ex]
-        self.round_graph = torch.cuda.CUDAGraph()
-        with torch.cuda.graph(self.round_graph):
-            for e in self.ex:
-                e(self.q, append=(self.k, self.v, tokens, tokens))
+        self.round_graphs = []
+        for lo in range(0, len(self.ex), 32):
+            gr = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(gr):
+                for e in self.ex[lo : lo + 32]:
+                    self._visit(e)
+            self.round_graphs.append(gr)
         for e, ring in zip(self.ex, rings):
             e.arenas.recent_len = ring
-        self.launches_per_step = 1
+        # and one graph of several rounds (about as many launches as a model has layers), used while every
+        # window has room for them: launches inside a graph are chained by programmatic dependent launch, two graph
+        # replays are not
+        self.chain_rounds = max(1, 32 // len(self.ex)) if append else max(1, 128 // len(self.ex))
+        self.chain_graph = None
+        if self.chain_rounds > 1:
+            self.chain_graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(self.chain_graph):
+                for _ in range(self.chain_rounds):
+                    for e in self.ex:
+                        self._visit(e)
+            for e, ring in zip(self.ex, rings):
+                e.arenas.recent_len = ring
+        self.launches_per_visit = 1
         self.launches_per_flush = 3
         a = self.ex[0].arenas
         self.geom = (a.n_fp, a.n_i4, a.i2_active)
 
+    def _visit(self, e):
+        if self.append:
+            e(self.q, append=(self.k, self.v, self.tokens, self.tokens))
+            if self.batch == 1:
+                e.arenas.recent_len += 1
+        else:
+            e(self.q)
 
-    def step_bytes(self, ring_len):
-        return algorithmic_bytes(*self.geom, ring_len, self.batch)
+    def visit_bytes(self, ring_len):
+        return algorithmic_bytes(*self.geom, ring_len, self.batch, self.hq, self.hkv, self.append)
+
+    def _account(self, a, t):
+        """Host bookkeeping of one visit of set t: flush if the window is full; returns (bytes, flushed)."""
+        flushed = 0
+        if self.append and a.recent_len == RING:
+            self.flush_graphs[t].replay()
+            a.recent_len = 0
+            flushed = 1
+        ring_after = a.recent_len + (1 if self.append else 0)
+        nbytes = self.visit_bytes(ring_after)
+        if self.append:
+            a.recent_len += 1
+        return nbytes, flushed
 
     def run_graph_steps(self, steps, start=0):
         """Enqueue `steps` steps; returns (bytes moved, decode launches, flushes)."""
         total, flushes = 0, 0
-        n, i, end = len(self.ex), start, start + steps
+        n = len(self.ex)
+        i, end = start * self.visits_per_step, (start + steps) * self.visits_per_step
         while i < end:
             s = i % n
             whole_round = s == 0 and i + n <= end
+            r = self.chain_rounds
+            if whole_round and self.chain_graph is not None and i + r * n <= end and \
+                    (not self.append or all(e.arenas.recent_len + r <= RING for e in self.ex)):
+                for e in self.ex:      # r rounds without a flush: one replay of the chained graph
+                    a = e.arenas
+                    for _ in range(r):
+                        total += self.visit_bytes(a.recent_len + (1 if self.append else 0))
+                        if self.append:
+                            a.recent_len += 1
+                self.chain_graph.replay()
+                i += r * n
+                continue
             for t in (range(n) if whole_round else (s,)):
-                a = self.ex[t].arenas
-                if a.recent_len == RING:
-                    self.flush_graphs[t].replay()
-                    a.recent_len = 0
-                    flushes += 1
-                total += self.step_bytes(a.recent_len + 1)
-                a.recent_len += 1
+                nbytes, flushed = self._account(self.ex[t].arenas, t)
+                total += nbytes
+                flushes += flushed
             if whole_round:
-                self.round_graph.replay()
+                for gr in self.round_graphs:
+                    gr.replay()
                 i += n
             else:
                 self.step_graphs[s].replay()
                 i += 1
-        return total, steps, flushes
+        return total, steps * self.visits_per_step, flushes
 
     def run_api_steps(self, steps, host_in, host_out, start=0, torch_copies=False):
-        """Public operator call with host buffers, one call per step (SplitKExecutor.step_host = r2k_decode_host):
+        """Public operator call with host buffers, one call per visit (SplitKExecutor.step_host = r2k_decode_host):
         H2D of q/k/v from pinned memory, decode+append, D2H of the output, wait.  `torch_copies` issues the same
-        step as three torch calls around the device-tensor operator instead (timed beside it for comparison)."""
+        visit as three torch calls around the device-tensor operator instead (timed beside it for comparison)."""
         total = 0
         nq, nk = self.q.numel(), self.k.numel()
         dev_in = self._dev_in
-        for i in range(start, start + steps):
+        first, last = start * self.visits_per_step, (start + steps) * self.visits_per_step
+        for i in range(first, last):
             s = i % len(self.ex)
             e = self.ex[s]
             a = e.arenas
-            if a.recent_len == RING:
+            if self.append and a.recent_len == RING:
                 self.R.flush_recent(a)
                 a.k_active, a.i2_active = self.base[s]
-            total += self.step_bytes(a.recent_len + 1)
+            total += self.visit_bytes(a.recent_len + (1 if self.append else 0))
+            idx = (self.tokens + i, self.tokens + i) if self.append else None
             if not torch_copies:
-                e.step_host(host_in, host_out, append_indices=(self.tokens + i, self.tokens + i))
+                e.step_host(host_in, host_out, append_indices=idx)
+                if self.append and self.batch == 1:
+                    a.recent_len += 1
                 continue
             dev_in.copy_(host_in, non_blocking=True)
-            q = dev_in[:nq].view(self.batch, HQ, D)
-            k = dev_in[nq : nq + nk].view(self.batch, HKV, D)
-            v = dev_in[nq + nk :].view(self.batch, HKV, D)
-            out = e(q, append=(k, v, self.tokens + i, self.tokens + i))
+            q = dev_in[:nq].view(self.batch, self.hq, D)
+            if self.append:
+                k = dev_in[nq : nq + nk].view(self.batch, self.hkv, D)
+                v = dev_in[nq + nk :].view(self.batch, self.hkv, D)
+                out = e(q, append=(k, v, idx[0], idx[1]))
+                if self.batch == 1:
+                    a.recent_len += 1
+            else:
+                out = e(q)
             host_out.copy_(out, non_blocking=True)
             torch.cuda.current_stream(self.device).synchronize()   # the caller reads the result
         return total
 
     def prepare_api(self):
-        n = self.q.numel() + 2 * self.k.numel()
+        n = self.q.numel() + (2 * self.k.numel() if self.append else 0)
         host_in = torch.empty(n, dtype=torch.bfloat16).pin_memory()
         host_in[: self.q.numel()] = self.q.flatten().cpu()
-        host_in[self.q.numel() : self.q.numel() + self.k.numel()] = self.k.flatten().cpu()
-        host_in[self.q.numel() + self.k.numel() :] = self.v.flatten().cpu()
-        host_out = torch.empty(self.batch, HQ, D, dtype=torch.bfloat16).pin_memory()
+        if self.append:
+            host_in[self.q.numel() : self.q.numel() + self.k.numel()] = self.k.flatten().cpu()
+            host_in[self.q.numel() + self.k.numel() :] = self.v.flatten().cpu()
+        host_out = torch.empty(self.batch, self.hq, D, dtype=torch.bfloat16).pin_memory()
         self._dev_in = torch.empty(n, dtype=torch.bfloat16, device=self.device)
         return host_in, host_out
+
+    def oracle_cache(self, s, b):
+        """The oracle's cache of request b of set s in the state the benchmark has left the GPU cache in: the static
+        pools as built (flushes of the benchmark overwrite rows outside the attended extent) plus a residual
+        window of `recent_len` copies of the request's appended row."""
+        from oracle import sspa_oracle as O
+        seed = self.seed0 + s
+        classes = page_classes(self.tokens // self.page, seed, self.mix[0], self.mix[1])
+        key, value = synth_kv(self.tokens, seed * 1000 + b, self.device, hkv=self.hkv)
+        cache = O.build_cache(key.cpu(), value.cpu(), classes, page_size=self.page, recent_capacity=RING, k_block=K_BLOCK,
+                              v2_group=V2_GROUP, append_capacity=RING)
+        k, v = self.k[b].cpu(), self.v[b].cpu()
+        for i in range(self.ex[s].arenas.recent_len):
+            O.append_token(cache, k, v, self.tokens + i, self.tokens + i)
+        return cache
+
+    def parity(self, requests=None, s=0):
+        """One decode (no append) of set s on the benchmarked caches against the oracle, for the given requests."""
+        from oracle import sspa_oracle as O
+        e = self.ex[s]
+        requests = sorted(set(requests if requests is not None else (0, self.batch - 1)))
+        out = e.decode_f32(self.q).cpu()
+        worst_abs, worst_excess = 0.0, -1.0
+        for b in requests:
+            want = O.decode_fp32(self.q[b : b + 1].float().cpu(), self.oracle_cache(s, b))
+            err, excess = tolerance_excess(out[b : b + 1], want)
+            worst_abs, worst_excess = max(worst_abs, err), max(worst_excess, excess)
+        return {"ok": bool(worst_excess <= 0 and e.device_status() == 0), "max_abs_err": float(f"{worst_abs:.3e}"),
+                "tolerance": f"max-abs {ATOL} + rel {RTOL}", "checked": f"requests {requests} of cache set {s} after the timed "
+                f"regions ({self.tokens} tokens + {e.arenas.recent_len} residual), fp32 output against the CPU oracle"}
 
 
 def time_region(device, fn, dist_on):
@@ -275,11 +453,12 @@ def time_region(device, fn, dist_on):
     return ms, result
 
 
-def sharded_1m(device, rank, world, steps, warmup, dist_on):
+def sharded_1m(device, rank, world, steps, warmup, dist_on, check=True):
     """Sequence-sharded decode of a 1,048,576-token cache (INT4/INT2 value pages 50/50,
     128-token residual window on the last rank).  With more than one rank the merge is fused into the decode
     launch (peer stores over NVLink, r2k_decode_exchange); the all-gather + merge-launch variant is timed
-    beside it for comparison."""
+    beside it for comparison.  Every variant's output is compared with the oracle: every rank runs the oracle's
+    un-normalised state over its own shard on the host, the states are gathered and merged in rank order."""
     import torch.distributed as dist
 
     import r2omni_b200 as R
@@ -292,10 +471,12 @@ def sharded_1m(device, rank, world, steps, warmup, dist_on):
     cache = R.build_three_precision_cache(key, value, make_plan(classes, PAGE, RING), page_size=PAGE,
                                           key_quantization_superblock=K_BLOCK, int2_group_size=V2_GROUP,
                                           compact_key_append_capacity=RING, recent_flush_size=RING)
+    host_kv = (key.cpu(), value.cpu()) if check else None
     del key, value
     ex = R.prepare_splitk_executor(cache, R.allocate_splitk_workspace(cache, num_query_heads=HQ))
     g = torch.Generator(device=device).manual_seed(6)
     q = torch.randn(1, HQ, D, generator=g, device=device).to(torch.bfloat16)
+    nk = None
     if rank == world - 1:
         st = R.DynamicCacheStats()
         nk = torch.randn(RING, HKV, 1, D, generator=g, device=device).to(torch.bfloat16)
@@ -304,8 +485,10 @@ def sharded_1m(device, rank, world, steps, warmup, dist_on):
                                      logical_position=total + i, stats=st)
     a = cache.arenas
     my_bytes = algorithmic_bytes(a.n_fp, a.n_i4, a.i2_active, a.recent_len, 1, append=False)
-    def timed(one_step, steps):
-        """(us per step, graphed?) for `steps` steps; eight steps per CUDA graph, eager launches if capture is refused."""
+
+    def timed(one_step, steps, repeats=5):
+        """(median us per step, graphed?, steps, spread) over `repeats` timed regions of `steps` steps; eight steps
+        per CUDA graph, eager launches if capture is refused."""
         for _ in range(max(warmup, 3)):
             one_step()
         torch.cuda.synchronize(device)
@@ -320,23 +503,29 @@ def sharded_1m(device, rank, world, steps, warmup, dist_on):
         except Exception:
             graph = None
             torch.cuda.synchronize(device)
-        if graph is not None:
-            steps = max(per_replay, steps // per_replay * per_replay)
-            ms, _ = time_region(device, lambda: [graph.replay() for _ in range(steps // per_replay)], dist_on)
-        else:
-            ms, _ = time_region(device, lambda: [one_step() for _ in range(steps)], dist_on)
-        return ms * 1e3 / steps, graph is not None, steps
+        samples = []
+        for _ in range(repeats):
+            if graph is not None:
+                steps = max(per_replay, steps // per_replay * per_replay)
+                ms, _ = time_region(device, lambda: [graph.replay() for _ in range(steps // per_replay)], dist_on)
+            else:
+                ms, _ = time_region(device, lambda: [one_step() for _ in range(steps)], dist_on)
+            samples.append(ms * 1e3 / steps)
+        return statistics.median(samples), graph is not None, steps, spread(samples)
 
-    nccl_us = None
+    nccl_us, fused_out, gathered_out, us_spread = None, None, None, None
+    fused_error = None
     if world == 1:
-        us, graphed, steps = timed(lambda: ex(q), steps)
+        us, graphed, steps, us_spread = timed(lambda: ex(q), steps)
+        fused_out = ex.decode_f32(q).clone()
     else:
         gathered = R.SequenceShardedExecutor(ex)
-        local_us, _, _ = timed(lambda: ex.decode_state(q, out=gathered.state), steps)   # this rank's shard alone
-        nccl_us, _, _ = timed(lambda: gathered(q), steps)
+        local_us, _, _, _ = timed(lambda: ex.decode_state(q, out=gathered.state), steps)   # this rank's shard alone
+        nccl_us, _, _, _ = timed(lambda: gathered(q), steps)
+        gathered_out = gathered(q).clone()
         # the fused variant is the one reported; if it cannot be set up or times out on this box, every rank
         # agrees on that and the all-gather number is reported instead (with the reason)
-        fused_error, fused = None, None
+        fused = None
         try:
             fused = R.SequenceShardedExecutor(ex, fused=True, device_step_counter=True)
             fused(q)                                   # one step first: a broken exchange shows up as a bounded
@@ -345,7 +534,8 @@ def sharded_1m(device, rank, world, steps, warmup, dist_on):
             if float(probe.item()) != 0.0:
                 fused_error = "device-side timeout in the cross-rank wait"
             else:
-                us, graphed, steps = timed(lambda: fused(q), steps)
+                us, graphed, steps, us_spread = timed(lambda: fused(q), steps)
+                fused_out = fused(q).clone()
                 if ex.device_status() != 0:
                     fused_error = "device-side timeout in the cross-rank wait"
         except Exception as exc:   # noqa: BLE001 -- reported in the JSON line
@@ -357,6 +547,7 @@ def sharded_1m(device, rank, world, steps, warmup, dist_on):
         if float(ok.item()) < 1.0:
             us, graphed, steps = nccl_us, True, steps
             fused_error = fused_error or "another rank failed"
+            fused_out = None
     bytes_all = torch.tensor([float(my_bytes)], device=device, dtype=torch.float64)
     if dist_on:
         dist.all_reduce(bytes_all)
@@ -364,101 +555,311 @@ def sharded_1m(device, rank, world, steps, warmup, dist_on):
            "gbps": round(float(bytes_all.item()) / (us * 1e-6) / 1e9, 1), "steps": steps,
            "collective": "none" if world == 1 else "fused: tagged peer stores over NVLink inside the decode launch",
            "launches_per_step": 1, "cuda_graph": graphed}
+    if us_spread is not None:
+        out["us_per_step_spread"] = us_spread
     if nccl_us is not None:
         out["us_per_step_nccl_all_gather"] = round(nccl_us, 2)
         out["us_per_step_local_shard_only"] = round(local_us, 2)
         if fused_error:
             out.update(collective="nccl all_gather of [Hq,130] fp32 per rank", launches_per_step=2, fused_error=fused_error)
+    if check:
+        out["parity"] = sharded_parity(device, rank, world, dist_on, host_kv, classes, nk, total, q, fused_out, gathered_out)
     return out
 
 
-def cpu_baseline_sample(tokens, seconds=12.0):
-    """The oracle (a port of the reference's dequantise-then-attend CPU path) on ONE
-    request of the workload, all host threads."""
+def sharded_parity(device, rank, world, dist_on, host_kv, classes, nk, total, q, fused_out, gathered_out):
+    """Every rank: the oracle's un-normalised (max, sum-exp, out) over its own shard, on the host; then one gather
+    and the oracle's merge in rank order on every rank.  The GPU outputs (fused exchange, all-gather variant) are
+    held against that, and against each other bit for bit."""
+    import torch.distributed as dist
     from oracle import sspa_oracle as O
-    torch.set_num_threads(os.cpu_count() or 1)
-    classes = page_classes(tokens // PAGE, 11, 0.25, 0.5)
-    key, value = synth_kv(tokens, 11000, "cpu")
-    cache = O.build_cache(key, value, classes, page_size=PAGE, recent_capacity=RING, k_block=K_BLOCK, v2_group=V2_GROUP,
-                          append_capacity=RING)
-    g = torch.Generator().manual_seed(5)
-    nk = torch.randn(RING // 2, HKV, D, generator=g).to(torch.bfloat16)
-    for i in range(RING // 2):
-        O.append_token(cache, nk[i], nk[i], tokens + i, tokens + i)
-    q = torch.randn(1, HQ, D, generator=g).to(torch.bfloat16)
-    O.decode(q, cache)
-    best, reps, t_end = float("inf"), 0, time.perf_counter() + seconds
-    while time.perf_counter() < t_end or reps < 3:
+    torch.set_num_threads(max(1, (os.cpu_count() or 1) // max(world, 1)))
+    per = host_kv[0].shape[1]
+    shard = O.build_cache(host_kv[0], host_kv[1], classes, page_size=PAGE, recent_capacity=RING, k_block=K_BLOCK,
+                          v2_group=V2_GROUP, append_capacity=RING)
+    if nk is not None:
+        rows = nk.cpu()
+        for i in range(RING):
+            O.append_token(shard, rows[i][:, 0], rows[(i + 1) % RING][:, 0], total + i, total + i)
+    top, den, acc = O.decode_state(q.float().cpu(), shard, chunk=65536)
+    state = torch.cat((top.unsqueeze(-1), den.unsqueeze(-1), acc), -1).contiguous().to(device)   # [1,Hq,130]
+    states = torch.empty((world,) + tuple(state.shape), device=device)
+    if dist_on:
+        dist.all_gather_into_tensor(states, state)
+    else:
+        states[0] = state
+    merged = None
+    for s in states.cpu():
+        part = (s[..., 0], s[..., 1], s[..., 2:])
+        merged = part if merged is None else O.merge_state(merged, part)
+    want = merged[2] / merged[1].unsqueeze(-1)
+    res = {"tolerance": f"max-abs {ATOL} + rel {RTOL}",
+           "checked": f"oracle state of every rank's shard ({per} tokens) on the host, gathered and merged in rank order"}
+    flags = []
+    for name, got in (("fused" if world > 1 else "decode", fused_out), ("all_gather", gathered_out)):
+        if got is None:
+            continue
+        err, excess = tolerance_excess(got, want.to(torch.bfloat16) if got.dtype == torch.bfloat16 else want)
+        res[f"{name}_max_abs_err"] = float(f"{err:.3e}")
+        flags.append(excess <= 0)
+    if fused_out is not None and gathered_out is not None:
+        res["fused_equals_all_gather_bitwise"] = bool(torch.equal(fused_out.view(torch.int16), gathered_out.view(torch.int16)))
+        flags.append(res["fused_equals_all_gather_bitwise"])
+    ok = torch.tensor([1.0 if flags and all(flags) else 0.0], device=device)
+    if dist_on:
+        dist.all_reduce(ok, op=dist.ReduceOp.MIN)     # every rank holds the same output; all must agree
+    res["ok"] = bool(ok.item() > 0)
+    return res
+
+
+# --------------------------------------------------------------------------- #
+# CPU baselines
+# --------------------------------------------------------------------------- #
+class CpuRequest:
+    """One request of a workload on the host: the reference's own CPU path (its torch quantisers, append/flush
+    state machine and dequantise-then-attend decoder) when the reference is installed, else the oracle port."""
+
+    def __init__(self, w, horizon_steps):
+        self.w = w
+        hq, hkv, tokens, page = w["hq"], w["hkv"], w["tokens"], w["page"]
+        torch.set_num_threads(os.cpu_count() or 1)
+        classes = page_classes(tokens // page, 11, w["mix"][0], w["mix"][1])
+        key, value = synth_kv(tokens, 11000, "cpu", hkv=hkv)
+        g = torch.Generator().manual_seed(5)
+        self.nk = torch.randn(RING, hkv, D, generator=g).to(torch.bfloat16)
+        self.q = torch.randn(1, hq, D, generator=g).to(torch.bfloat16)
+        self.ns, self.why_port = load_reference()
+        self.kind = "reference" if self.ns is not None else "port"
+        # room for every flush of the run: the context grows by 128 tokens per flush
+        room = RING * (horizon_steps // RING + 2)
+        if self.ns is not None:
+            ns = self.ns
+            self.cache = ns.build_three_precision_cache(
+                key, value, reference_plan(ns, classes, page, RING), page_size=page, key_quantization_superblock=K_BLOCK,
+                int2_group_size=V2_GROUP, compact_key_append_capacity=room, recent_flush_size=RING)
+            self.stats = ns.DynamicCacheStats()
+        else:
+            from oracle import sspa_oracle as O
+            self.O = O
+            self.cache = O.build_cache(key, value, classes, page_size=page, recent_capacity=RING, k_block=K_BLOCK,
+                                       v2_group=V2_GROUP, append_capacity=room)
+        self.i = 0
+        for _ in range(RING // 2 if w["append"] else RING):
+            self.append()
+
+    def append(self):
+        i, t = self.i, self.w["tokens"]
+        k, v = self.nk[i % RING], self.nk[(i + 1) % RING]
+        if self.ns is not None:
+            self.ns.append_generated_token(self.cache, k.unsqueeze(1), v.unsqueeze(1), global_token_index=t + i,
+                                           logical_position=t + i, stats=self.stats)
+        else:
+            self.O.append_token(self.cache, k, v, t + i, t + i)
+        self.i += 1
+
+    def step(self):
+        """One decode step of the workload for this request; returns its algorithmic bytes."""
+        if self.w["append"]:
+            self.append()
+        if self.ns is not None:
+            self.ns.triton_mixed_reference(self.q, self.cache)
+            c = self.cache
+            n = (c.fp_pool.token_count, c.int4_pool.token_count, c.int2_pool.token_count, c.recent_fp_pool.token_count)
+        else:
+            self.O.decode(self.q, self.cache)
+            c = self.cache
+            n = (c.n_fp, c.n_i4, c.i2_active, c.recent_len)
+        return algorithmic_bytes(n[0], n[1], n[2], n[3], 1, self.w["hq"], self.w["hkv"], self.w["append"])
+
+    def describe(self):
+        what = ("the reference's own CPU path (triton_mixed_reference + append_generated_token, imported unmodified)"
+                if self.ns is not None else f"the oracle port ({self.why_port})")
+        return what
+
+
+def cpu_baseline_sample(w, seconds=12.0):
+    """A bounded sample of the workload on the host cores: ONE request of one layer, all host threads."""
+    req = CpuRequest(w, horizon_steps=4096)
+    req.step()
+    best, reps, t_end, nbytes = float("inf"), 0, time.perf_counter() + seconds, 0
+    while (time.perf_counter() < t_end or reps < 3) and reps < 4000:
         t0 = time.perf_counter()
-        O.append_token(cache, nk[0], nk[0], 0, 0) if cache.recent_len < RING else None
-        O.decode(q, cache)
+        nbytes = req.step()
         best = min(best, time.perf_counter() - t0)
         reps += 1
-    nbytes = algorithmic_bytes(cache.n_fp, cache.n_i4, cache.i2_active, cache.recent_len, 1)
-    return {"value": round(nbytes / best / 1e9, 3), "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
-            "sample": f"1 of 8 requests ({tokens} tokens, same page mix), best of {reps} decode+append steps, "
-                      f"{best * 1e3:.1f} ms per request-step"}
+    return {"value": round(nbytes / best / 1e9, 3), "unit": "GB/s", "cores": torch.get_num_threads(), "kind": req.kind,
+            "sample": f"1 of {w['batch']} requests of one layer ({w['tokens']} tokens, same page mix), best of {reps} "
+                      f"decode{'+append' if w['append'] else ''} steps, {best * 1e3:.2f} ms per request-step; {req.describe()}"}
 
 
 def run_reference_arm(args):
-    """The reference's CPU implementation of the path (oracle port; the reference is Python and
-    does not travel to the GPU box), all host threads, one request per step."""
-    from oracle import sspa_oracle as O
+    """The reference's CPU implementation of the path on the host cores (imported unmodified from baseline/_ref
+    when it is installed there, else the oracle port), all host threads, one request per step."""
     rank = int(os.environ.get("RANK", "0"))
     if rank != 0:
         return
-    torch.set_num_threads(os.cpu_count() or 1)
-    tokens = 32768
-    classes = page_classes(tokens // PAGE, 11, 0.25, 0.5)
-    key, value = synth_kv(tokens, 11000, "cpu")
-    cache = O.build_cache(key, value, classes, page_size=PAGE, recent_capacity=RING, k_block=K_BLOCK, v2_group=V2_GROUP,
-                          append_capacity=RING)
-    base = (cache.k_active, cache.i2_active)
-    g = torch.Generator().manual_seed(5)
-    nk = torch.randn(RING, HKV, D, generator=g).to(torch.bfloat16)
-    q = torch.randn(1, HQ, D, generator=g).to(torch.bfloat16)
-    for i in range(RING // 2):
-        O.append_token(cache, nk[i], nk[i], tokens + i, tokens + i)
+    w = WORKLOADS[args.workload]
     steps = min(args.steps, 200)
-
-    def step(i):
-        if O.append_token(cache, nk[i % RING], nk[(i + 1) % RING], tokens + i, tokens + i):
-            cache.k_active, cache.i2_active = base[0], base[1]     # keep the context at 32768 + residual
-            cache.i2_global, cache.i2_logical = cache.i2_global[: base[1]], cache.i2_logical[: base[1]]
-        O.decode(q, cache)
-        return algorithmic_bytes(cache.n_fp, cache.n_i4, cache.i2_active, cache.recent_len, 1)
-
-    for i in range(max(1, min(args.warmup, 3))):
-        step(i)
+    req = CpuRequest(w, horizon_steps=steps + 16)
+    for _ in range(max(1, min(args.warmup, 3))):
+        req.step()
     t0 = time.perf_counter()
-    nbytes = sum(step(10 + i) for i in range(steps))
+    nbytes = sum(req.step() for _ in range(steps))
     sec = time.perf_counter() - t0
     value = round(nbytes / sec / 1e9, 3)
+    sample = (f"one of the {w['batch']} requests of one layer per step ({w['tokens']} tokens, same page mix), decode"
+              f"{' + one-token append, flush when the residual window fills' if w['append'] else ''}; {req.describe()}")
     line = {
         "impl": "reference", "metric": METRIC, "value": value, "unit": "GB/s", "n_gpus": args.gpus, "steps": steps,
         "warmup": args.warmup, "ms_per_step": round(sec * 1e3 / steps, 3), "higher_is_better": True, "scaling": "weak",
-        "vs_baseline": None, "dtype": "bf16", "data": "synthetic",
-        "config": {"workload": "decode_32k_b8", "sample": "one request (32768 tokens) per step", "heads": "16q/2kv x128"},
-        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": "port",
-                         "sample": "one of the 8 requests per step (32768 tokens, bf16/INT4/INT2 pages 25/50/25), "
-                                   "decode + one-token append, flush when the residual window fills"},
+        "vs_baseline": None, "dtype": "f32 (dequantise-then-attend on the host)", "data": "synthetic",
+        "config": {"workload": args.workload, "sample": f"one request ({w['tokens']} tokens) per step",
+                   "heads": f"{w['hq']}q/{w['hkv']}kv x128"},
+        "cpu_baseline": {"value": value, "unit": "GB/s", "cores": torch.get_num_threads(), "kind": req.kind, "sample": sample},
         "e2e": {"value": value, "unit": "GB/s", "h2d_bytes_per_step": 0, "d2h_bytes_per_step": 0},
     }
     print(json.dumps(line))
 
 
+# --------------------------------------------------------------------------- #
+# the reference's Triton decoder on this GPU
+# --------------------------------------------------------------------------- #
+def triton_reference_record(device, bench, steps=200, sets=3):
+    """The reference's fused split-K decoder (Triton, JIT-compiled for this GPU) on the benchmark's workload, built
+    from the same seeds through the reference's own build_three_precision_cache -> allocate_splitk_workspace ->
+    prepare_splitk_executor -> stack_homogeneous_splitk_executors, launch policy as its attention manager
+    chooses it (block_n 64 beyond 6144 tokens, fp16 partials, hierarchical reduce), CUDA events around `steps`
+    eager steps over `sets` cache sets; plus the largest difference between its output and this library's on the
+    same state.  Any failure to import, compile or run is recorded as text instead."""
+    ns, why = load_reference()
+    if ns is None:
+        return {"unavailable": why}
+    try:
+        from r2omni.sspa.kernels import triton_fourq_splitk as T
+        w = dict(hq=bench.hq, hkv=bench.hkv, batch=bench.batch, tokens=bench.tokens, page=bench.page, mix=bench.mix)
+        block_n = 64 if w["tokens"] > 6144 else 128
+        stacked = []
+        t_build = time.perf_counter()
+        for s in range(sets):
+            seed = bench.seed0 + s
+            classes = page_classes(w["tokens"] // w["page"], seed, w["mix"][0], w["mix"][1])
+            singles = []
+            for b in range(w["batch"]):
+                key, value = synth_kv(w["tokens"], seed * 1000 + b, device, hkv=w["hkv"])
+                cache = ns.build_three_precision_cache(
+                    key, value, reference_plan(ns, classes, w["page"], RING, device), page_size=w["page"],
+                    key_quantization_superblock=K_BLOCK, int2_group_size=V2_GROUP, compact_key_append_capacity=RING,
+                    recent_flush_size=RING)
+                ws = T.allocate_splitk_workspace(cache, block_n=block_n, num_query_heads=w["hq"],
+                                                 partial_output_dtype=torch.float16, hierarchical_group_blocks=64)
+                singles.append(T.prepare_splitk_executor(
+                    cache, ws, block_n=block_n, num_warps=8, num_stages=1, reduce_num_warps=8 if block_n == 64 else 4,
+                    broadcast_k_metadata=True, use_tensor_cores_qk=True, use_tensor_cores_pv=False, output_hadamard=False,
+                    hierarchical_reduce=True))
+                del key, value
+            if s == 0:
+                probe = singles[0]       # request 0 alone: decoded by both libraries from the very same tensors below
+            stacked.append(T.stack_homogeneous_splitk_executors(singles) if w["batch"] > 1 else singles[0])
+            del singles
+        build_s = time.perf_counter() - t_build
+        q, k, v = bench.q, bench.k, bench.v
+        ring_target = bench.ex[0].arenas.recent_len     # bring set 0 to the state this library's set 0 is in
+        for s, ex in enumerate(stacked):
+            for i in range(ring_target if s == 0 else RING // 2):
+                ex(q, append=(k, v, w["tokens"] + i, w["tokens"] + i))
+        torch.cuda.synchronize(device)
+        theirs = stacked[0](q).float().clone()
+        ours = bench.ex[0](q).float().clone()
+        diff = float((theirs - ours).abs().max())
+        # the same bytes through both decoders: this library adopts the reference-built cache of request 0 in place
+        import r2omni_b200 as R
+        adopted = R.adopt_reference_cache(probe.cache)
+        mine = R.prepare_splitk_executor(adopted, R.allocate_splitk_workspace(adopted, num_query_heads=w["hq"]))
+        q0 = q[0:1].contiguous()
+        same_cache_diff = float((probe(q0).float() - mine(q0).float()).abs().max())
+        oracle_diff = float((ns.triton_mixed_reference(q0, probe.cache).float() - mine(q0).float()).abs().max())
+        # timed: decode without append (the window of a set would fill after 64 steps and the reference must then
+        # be unstacked to flush); the appended row is 0.5 % of the traffic
+        for _ in range(3):
+            for ex in stacked:
+                ex(q)
+        torch.cuda.synchronize(device)
+        e0, e1 = torch.cuda.Event(enable_timing=True), torch.cuda.Event(enable_timing=True)
+        samples = []
+        for _ in range(5):
+            e0.record()
+            for i in range(steps):
+                stacked[i % sets](q)
+            e1.record()
+            torch.cuda.synchronize(device)
+            samples.append(e0.elapsed_time(e1) * 1e3 / steps)
+        us = statistics.median(samples)
+        # the same calls captured into one CUDA graph (takes the Python launch path out of the measurement), if
+        # the reference's call can be captured at all
+        graph_us, graph_note = None, None
+        try:
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                for ex in stacked:
+                    ex(q)
+            graph.replay()
+            torch.cuda.synchronize(device)
+            gs = []
+            for _ in range(5):
+                e0.record()
+                for i in range(max(1, steps // sets)):
+                    graph.replay()
+                e1.record()
+                torch.cuda.synchronize(device)
+                gs.append(e0.elapsed_time(e1) * 1e3 / (max(1, steps // sets) * sets))
+            graph_us = statistics.median(gs)
+        except Exception as exc:  # noqa: BLE001
+            graph_note = f"not capturable: {exc!r}"[:200]
+            torch.cuda.synchronize(device)
+        a = bench.ex[0].arenas
+        nbytes = algorithmic_bytes(a.n_fp, a.n_i4, a.i2_active, RING // 2, w["batch"], w["hq"], w["hkv"], append=False)
+        import triton
+        best = min(us, graph_us) if graph_us is not None else us
+        return {"us_per_step": round(best, 2), "us_per_step_eager": round(us, 2), "us_per_step_spread_eager": spread(samples),
+                "us_per_step_cuda_graph": None if graph_us is None else round(graph_us, 2), "cuda_graph_note": graph_note,
+                "gbps": round(nbytes / (best * 1e-6) / 1e9, 1),
+                "launches_per_step": 3, "block_n": block_n, "triton": triton.__version__, "cache_sets": sets,
+                "max_abs_diff_same_cache": float(f"{same_cache_diff:.3e}"),
+                "max_abs_diff_same_cache_vs_reference_torch_decoder": float(f"{oracle_diff:.3e}"),
+                "max_abs_diff_own_caches": float(f"{diff:.3e}"),
+                "diff_note": "same_cache: request 0 of the reference-built cache decoded by the reference's Triton kernel and, "
+                             "adopted in place, by this library (bf16 outputs).  own_caches: each library decoding the cache it "
+                             "packed itself; the reference's Triton pack kernels break rounding ties differently from its "
+                             "torch pack routine (which this library reproduces bit for bit), so the two caches differ",
+                "steps": steps, "build_seconds": round(build_s, 1),
+                "what": "reference SplitKExecutor.__call__ (stacked batch, no append) on the same seeded caches, eager "
+                        "launches from Python and replayed from a CUDA graph; this library's comparable figure is "
+                        "roofline.us_per_launch_isolated"}
+    except Exception as exc:  # noqa: BLE001 -- the record of the failure is the deliverable
+        import traceback
+        return {"error": repr(exc)[:400], "where": traceback.format_exc().strip().splitlines()[-3:]}
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
-    ap.add_argument("--steps", type=int, default=8192)
+    ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=16)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode_32k_b8", choices=["decode_32k_b8", "small"])
+    ap.add_argument("--workload", default="decode_32k_b8", choices=sorted(WORKLOADS))
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sharded", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
-    ap.add_argument("--page-mix", default="25,50,25", help="percent of bf16,INT4,INT2 value pages (kernel studies)")
+    ap.add_argument("--no-parity", action="store_true")
+    ap.add_argument("--no-triton-reference", action="store_true")
+    ap.add_argument("--page-mix", default=None, help="percent of bf16,INT4,INT2 value pages (kernel studies)")
     args = ap.parse_args()
+    w = dict(WORKLOADS[args.workload])
+    if args.steps is None:
+        args.steps = {"decode_7b_28l": 256, "decode_4k_b1": 16384}.get(args.workload, 8192)
+    if args.page_mix is not None:
+        mix = [float(x) / 100.0 for x in args.page_mix.split(",")]
+        w["mix"] = (mix[0], mix[1])
     if args.impl == "reference":
         run_reference_arm(args)
         return
@@ -475,104 +876,148 @@ def main():
     L.lib()   # fails loudly when the CUDA library is missing: there is no fallback
 
     warmup = max(args.warmup, 3)
-    tokens, batch = (32768, 8) if args.workload == "decode_32k_b8" else (4096, 2)
-    mix = [float(x) / 100.0 for x in args.page_mix.split(",")]
-    bench = ReplicaBench(device, batch=batch, tokens=tokens, sets=4, p_fp=mix[0], p_i4=mix[1])
+    default_workload = args.workload == "decode_32k_b8" and args.page_mix is None
+    bench = ReplicaBench(device, hq=w["hq"], hkv=w["hkv"], batch=w["batch"], tokens=w["tokens"], sets=w["sets"],
+                         page=w["page"], mix=w["mix"], step=w["step"], append=w["append"])
+    n_sets, vps = len(bench.ex), bench.visits_per_step
     bench.run_graph_steps(warmup)
-    launches0 = L.lib().r2k_launch_count()
     with ClockSampler(local) as clocks:
         ms, (nbytes, decodes, flushes) = time_region(device, lambda: bench.run_graph_steps(args.steps, start=warmup), dist_on)
     value = nbytes * world / (ms * 1e-3) / 1e9
-    gpu_launches = decodes * bench.launches_per_step + flushes * bench.launches_per_flush
+    gpu_launches = decodes * bench.launches_per_visit + flushes * bench.launches_per_flush
 
     # the decode kernel alone: same graphs, no flush in the window
-    probe_steps = 0
+    probe_visits = 0
+    rounds = 32 if w["append"] else 8      # visits of every set inside the window (it must fit the residual window)
+    rounds = max(bench.chain_rounds, rounds // bench.chain_rounds * bench.chain_rounds)
     def make_room():
+        if not w["append"]:
+            return
         for s, e in enumerate(bench.ex):
-            if e.arenas.recent_len > RING - 33:
+            if e.arenas.recent_len > RING - rounds - 1:
                 bench.flush_graphs[s].replay()
                 e.arenas.recent_len = 0
-    def decode_only(rounds=True):
-        nonlocal probe_steps
+    def decode_only(whole_rounds=True):
+        nonlocal probe_visits
         b = 0
-        for r in range(32):
+        for r in range(rounds):
             for e in bench.ex:
-                b += bench.step_bytes(e.arenas.recent_len + 1)
-                e.arenas.recent_len += 1
-                probe_steps += 1
-            if rounds:
-                bench.round_graph.replay()
-            else:
+                b += bench.visit_bytes(e.arenas.recent_len + (1 if w["append"] else 0))
+                if w["append"]:
+                    e.arenas.recent_len += 1
+                probe_visits += 1
+            if not whole_rounds:
                 for g in bench.step_graphs:
                     g.replay()
+            elif bench.chain_graph is None:
+                for gr in bench.round_graphs:
+                    gr.replay()
+            elif (r + 1) % bench.chain_rounds == 0:
+                bench.chain_graph.replay()
         return b
     # launches separated by graph boundaries (no overlap between consecutive launches), for comparison
     make_room()
     iso_ms, _ = time_region(device, lambda: decode_only(False), dist_on)
-    iso_us = iso_ms * 1e3 / max(probe_steps, 1)
-    probe_steps = 0
+    iso_us = iso_ms * 1e3 / max(probe_visits, 1)
+    probe_visits = 0
     make_room()
     k_ms, k_bytes = time_region(device, decode_only, dist_on)
     peak, peak_kind = measured_peak_gbs()
     achieved = k_bytes / (k_ms * 1e-3) / 1e9
     roofline = {"bound": "hbm", "kernel": "decode_kernel<bf16>", "achieved": round(achieved, 1), "peak": peak,
                 "peak_source": peak_kind, "unit": "GB/s", "frac": round(achieved / peak, 4),
-                "frac_of_nominal_8000": round(achieved / 8000.0, 4), "us_per_launch": round(k_ms * 1e3 / max(probe_steps, 1), 2),
+                "frac_of_nominal_8000": round(achieved / 8000.0, 4), "us_per_launch": round(k_ms * 1e3 / max(probe_visits, 1), 2),
                 "us_per_launch_isolated": round(iso_us, 2),
-                "bytes_per_launch": int(k_bytes / max(probe_steps, 1)),
-                "traffic": NCU_DRAM_BYTES_PER_LAUNCH if args.workload == "decode_32k_b8" and args.page_mix == "25,50,25" else None}
+                "bytes_per_launch": int(k_bytes / max(probe_visits, 1)),
+                "traffic": NCU_DRAM_BYTES_PER_LAUNCH if default_workload else None}
 
     # the flush alone (quantize-and-pack of the 128-token residual window: 3 launches, launch-bound)
-    def flush_only():
-        for r in range(8):
-            for s_, e in enumerate(bench.ex):
-                bench.flush_graphs[s_].replay()
-                e.arenas.recent_len = 0
-    f_ms, _ = time_region(device, flush_only, dist_on)
-    flush = {"us_per_flush": round(f_ms * 1e3 / (8 * len(bench.ex)), 2), "launches": bench.launches_per_flush,
-             "amortised_us_per_step": round(f_ms * 1e3 / (8 * len(bench.ex)) / RING, 3)}
+    flush = None
+    if w["append"]:
+        def flush_only():
+            for r in range(8):
+                for s_, e in enumerate(bench.ex):
+                    bench.flush_graphs[s_].replay()
+                    e.arenas.recent_len = 0
+        f_ms, _ = time_region(device, flush_only, dist_on)
+        flush = {"us_per_flush": round(f_ms * 1e3 / (8 * n_sets), 2), "launches": bench.launches_per_flush,
+                 "amortised_us_per_step": round(f_ms * 1e3 / (8 * n_sets) / RING * vps, 3)}
 
     # end to end through the operator call with host buffers
     e2e = None
     if not args.no_e2e:
         host_in, host_out = bench.prepare_api()
-        bench.run_api_steps(warmup, host_in, host_out)
-        e2e_steps = min(args.steps, 512)
-        e_ms, e_bytes = time_region(device, lambda: bench.run_api_steps(e2e_steps, host_in, host_out, start=warmup), dist_on)
-        e2e = {"value": round(e_bytes * world / (e_ms * 1e-3) / 1e9, 1), "unit": "GB/s",
-               "us_per_step": round(e_ms * 1e3 / e2e_steps, 2), "steps": e2e_steps,
-               "h2d_bytes_per_step": int(host_in.numel() * 2), "d2h_bytes_per_step": int(host_out.numel() * 2),
-               "call": "SplitKExecutor.step_host (r2k_decode_host): H2D copy kernel from the pinned block, decode+append writing the pinned result over PCIe, stream wait"}
-        t_steps = min(e2e_steps, 256)
-        t_ms, _ = time_region(device, lambda: bench.run_api_steps(t_steps, host_in, host_out, start=warmup + e2e_steps,
-                                                                  torch_copies=True), dist_on)
+        bench.run_api_steps(max(1, warmup // vps), host_in, host_out)
+        e2e_steps = max(1, min(args.steps, 512 // vps))
+        cursor = warmup
+        samples, e_bytes_ms = [], []
+        for _ in range(5):
+            e_ms, e_bytes = time_region(device, lambda: bench.run_api_steps(e2e_steps, host_in, host_out, start=cursor), dist_on)
+            cursor += e2e_steps
+            samples.append(e_ms * 1e3 / e2e_steps)
+            e_bytes_ms.append(e_bytes / (e_ms * 1e-3))
+        e_us = statistics.median(samples)
+        e2e = {"value": round(statistics.median(e_bytes_ms) * world / 1e9, 1), "unit": "GB/s",
+               "us_per_step": round(e_us, 2), "us_per_step_spread": spread(samples), "steps": e2e_steps,
+               "h2d_bytes_per_step": int(host_in.numel() * 2 * vps), "d2h_bytes_per_step": int(host_out.numel() * 2 * vps),
+               "call": "SplitKExecutor.step_host (r2k_decode_host), one call per launch: H2D copy kernel from the pinned block, "
+                       "decode+append writing the pinned result over PCIe, stream wait"}
+        t_steps = max(1, min(e2e_steps, 256 // vps))
+        t_ms, _ = time_region(device, lambda: bench.run_api_steps(t_steps, host_in, host_out, start=cursor, torch_copies=True),
+                              dist_on)
         e2e["us_per_step_three_torch_calls"] = round(t_ms * 1e3 / t_steps, 2)
+
+    parity = None
+    if not args.no_parity:
+        ok_local = bench.parity()
+        flag = torch.tensor([1.0 if ok_local["ok"] else 0.0], device=device)
+        if dist_on:
+            dist.all_reduce(flag, op=dist.ReduceOp.MIN)
+            ok_local["ok"] = bool(flag.item() > 0)
+            ok_local["checked"] += "; every rank checks its own replica"
+        parity = ok_local
+
+    triton_ref = None
+    if rank == 0 and world == 1 and not args.no_triton_reference and args.workload in ("decode_32k_b8", "small"):
+        triton_ref = triton_reference_record(device, bench)
+
+    config_note = bench_bytes_note(w)
+    chain_launches = bench.chain_rounds * n_sets
+    set_mb = bench.visit_bytes(RING) / 1e6
     del bench
     torch.cuda.empty_cache()
 
     sharded = None if args.no_sharded or args.workload != "decode_32k_b8" else \
-        sharded_1m(device, rank, world, steps=min(args.steps, 256), warmup=warmup, dist_on=dist_on)
+        sharded_1m(device, rank, world, steps=min(args.steps, 256), warmup=warmup, dist_on=dist_on, check=not args.no_parity)
     cpu = None
     if rank == 0 and world == 1 and not args.no_cpu_baseline:
-        cpu = cpu_baseline_sample(tokens)
+        cpu = cpu_baseline_sample(w)
 
     if rank == 0:
+        mix_pct = ",".join(str(int(round(100 * x))) for x in (w["mix"][0], w["mix"][1], 1.0 - w["mix"][0] - w["mix"][1]))
         line = {
             "metric": METRIC, "value": round(value, 1), "unit": "GB/s", "n_gpus": world, "steps": args.steps, "warmup": warmup,
             "ms_per_step": round(ms / args.steps, 5), "us_per_step": round(ms * 1e3 / args.steps, 2), "higher_is_better": True,
             "scaling": "weak", "vs_baseline": None, "dtype": "f16 tensor-core products, f32 accumulation (u4/u2 codes, bf16 pages)",
             "data": "synthetic",
-            "config": {"workload": args.workload, "batch_per_gpu": batch, "tokens_per_request": tokens, "heads": "16q/2kv x128",
-                       "pages": f"64 tokens; bf16/INT4/INT2 = {args.page_mix} % from a seed", "keys": "INT4 per channel, 32-token blocks",
-                       "residual_window": RING, "append_per_step": 1, "flush_every": RING,
-                       "l2": "4 cache sets of ~98 MB visited round-robin (inputs larger than L2)",
+            "config": {"workload": args.workload, "batch_per_gpu": w["batch"], "tokens_per_request": w["tokens"],
+                       "heads": f"{w['hq']}q/{w['hkv']}kv x128", "layers": n_sets if w["step"] == "round" else 1,
+                       "pages": f"{w['page']} tokens; bf16/INT4/INT2 = {mix_pct} % from a seed",
+                       "keys": "INT4 per channel, 32-token blocks",
+                       "residual_window": RING, "append_per_step": 1 if w["append"] else 0,
+                       "flush_every": RING if w["append"] else None,
+                       "step": "one decode launch" if vps == 1 else f"{vps} decode launches (all layers)",
+                       "l2": f"{n_sets} cache sets of ~{set_mb:.1f} MB visited in order (inputs larger than L2)",
+                       "graphs": f"{chain_launches} decode launches per CUDA-graph replay, chained by programmatic dependent launch",
                        "parallelism": f"{world} independent replicas" if world > 1 else "1 GPU",
-                       "step_bytes": bench_bytes_note(tokens, batch)},
-            "gpu_launches": int(gpu_launches), "flushes_in_region": int(flushes), "flush": flush,
-            "roofline": roofline, "e2e": e2e, "clocks": clocks.summary(),
+                       "step_bytes": config_note},
+            "gpu_launches": int(gpu_launches), "flushes_in_region": int(flushes),
+            "flush": flush, "roofline": roofline, "e2e": e2e, "parity": parity, "clocks": clocks.summary(),
         }
         if cpu is not None:
             line["cpu_baseline"] = cpu
+        if triton_ref is not None:
+            line["triton_reference"] = triton_ref
         if sharded is not None:
             line["seq_sharded"] = sharded
         print(json.dumps(line))
@@ -580,8 +1025,9 @@ def main():
         dist.destroy_process_group()
 
 
-def bench_bytes_note(tokens, batch):
-    return f"sum over {batch} requests x 2 kv heads of 76 B/token keys + 256/68/44 B/token values + 512 B/residual token"
+def bench_bytes_note(w):
+    return (f"sum over {w['batch']} requests x {w['hkv']} kv heads of 76 B/token keys + 256/68/44 B/token values + "
+            "512 B/residual token" + (f", x {w['sets']} layers per step" if w["step"] == "round" else ""))
 
 
 if __name__ == "__main__":

@@ -14,7 +14,7 @@ constexpr int kThreads = (kNW + 1) * 32;    // plus one producer warp
 constexpr int kConsumers = kNW * 32;
 constexpr int kTQ = kNW * 32;               // tokens per tile: INT4-/INT2-value pools (one key block per warp)
 constexpr int kTF = kNW * 16;               // tokens per tile: bf16-value pool
-constexpr int kTR = 32;                     // tokens per tile: residual window (two warps)
+constexpr int kTR = (kNW / 2) * 16;         // tokens per tile: residual window (16 per warp of one half of the warps)
 constexpr int kStages = 3;
 constexpr int kCtasPerSm = 1;
 

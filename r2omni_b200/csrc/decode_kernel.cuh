@@ -610,6 +610,14 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const __gr
   const int g = lane >> 2, t = lane & 3, pg = pi_row(g);
   bool alive = true;
   WarpState st;
+  // the partition arithmetic of the first (request, kv head) needs nothing a previous kernel wrote: done while
+  // that kernel is still finishing, it is off the path from the dependency wait to the first tile
+  int first_u0 = 0, first_u1 = 0, first_part0 = 0, first_nparts = 1;
+  if (bh_lo <= bh_hi) {
+    unit_range(p, c0, c1, bh_lo, first_u0, first_u1);
+    first_part0 = first_cta_of(p, bh_lo);
+    first_nparts = last_cta_of(p, bh_lo) - first_part0 + 1;
+  }
   grid_dependency_wait();
   // step tag of the fused cross-rank merge: read once, here, by everybody (see the counter hand-over below)
   const uint32_t xstep = p.xw > 1 ? exchange_step(p) : 0u;
@@ -617,14 +625,17 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const __gr
 
   for (int bh = bh_lo; bh <= bh_hi; ++bh) {
     const int b = bh / p.g.num_kv_heads, h = bh - b * p.g.num_kv_heads;
-    int u0, u1;
-    unit_range(p, c0, c1, bh, u0, u1);
+    int u0 = first_u0, u1 = first_u1;
+    // who else works on this head: known before the first tile arrives, so it is off the path to the merge
+    int part0 = first_part0, nparts = first_nparts;
+    if (bh != bh_lo) {
+      unit_range(p, c0, c1, bh, u0, u1);
+      part0 = first_cta_of(p, bh);
+      nparts = last_cta_of(p, bh) - part0 + 1;
+    }
     const int rlen0 = *reinterpret_cast<const int*>((const uint8_t*)p.v.recent_len + (size_t)b * p.v.recent_len_bstride);
     const int rlen = rlen0 + (has_append ? 1 : 0);
     state_reset(st);
-    // who else works on this head: known before the first tile arrives, so it is off the path to the merge
-    const int part0 = first_cta_of(p, bh);
-    const int nparts = last_cta_of(p, bh) - part0 + 1;
 
     // query fragments of head g of this KV group, channels 32t..32t+31
     const uint16_t* qrow = nullptr;
@@ -648,10 +659,12 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const __gr
                           qh, warp, lane);
     consume_pool<2, BF16>(st, p, max(u0, p.nF + p.n4), min(u1, p.nF + p.n4 + p.n2), p.nF + p.n4, stage0, full_bar, empty_bar,
                           stage, phase, alive, qh, warp, lane);
-    // residual window: 32-token tiles, 16 tokens for each of warps 0 and 1
+    // residual window: kTR-token tiles, 16 tokens per warp; the lower half of the warps takes even tiles and the
+    // upper half odd ones, so two tiles (the whole 128-token window) are in work at once
     set_units(st, 0);
     for (int u = max(u0, p.nF + p.n4 + p.n2); u < u1; ++u) {
-      const int win = (u - p.nF - p.n4 - p.n2) * kTR;
+      const int ur = u - p.nF - p.n4 - p.n2;
+      const int win = ur * kTR;
       if (win >= rlen) continue;
       if (alive && !mbar_wait(&full_bar[stage], phase)) {
         if (lane == 0) atomicExch(p.err, R2K_ERR_DEVICE_TIMEOUT);
@@ -660,8 +673,8 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const __gr
       if (alive) {
         uint8_t* sbp = stages + stage * kStageBytes;
         const uint32_t sb = stage0 + stage * kStageBytes;
-        if (warp < 2) {
-          const int r0 = 16 * warp;
+        if ((warp >= kNW / 2 ? 1 : 0) == (ur & 1)) {
+          const int r0 = 16 * (warp % (kNW / 2));
           const int hi = min(rlen - win - r0, 16);
           if (hi > 0) {
             const int app_row = rlen0 - win - r0;  // ring row that receives the appended token, relative to this slice

@@ -1,6 +1,7 @@
 // extern "C" surface of libr2k_b200.so: validation, launch geometry, launches.
 // No torch types, no allocation, no synchronisation (except r2k_decode_device_status).
 #include <atomic>
+#include <cstdio>
 #include <cstdlib>
 #include <cstring>
 #include <mutex>
@@ -103,7 +104,14 @@ int derive(const R2KGeom* g, DecodeParams* p) {
   // are measured per-tile times (ns of one CTA slot on B200, pure-pool caches), scaled down until a whole
   // (request, kv head) fits in 22 bits: the kernel's partition arithmetic is 32-bit.
   (void)g2;
-  const double ns[4] = {1400.0, 2110.0, 2400.0, 450.0};
+  double ns[4] = {1400.0, 2110.0, 2400.0, 500.0};
+  // R2K_TILE_NS="bf16,int4,int2,residual" in the environment overrides the weights (tuning runs)
+  static const char* tile_ns_env = std::getenv("R2K_TILE_NS");
+  if (tile_ns_env != nullptr) {
+    double v[4];
+    if (std::sscanf(tile_ns_env, "%lf,%lf,%lf,%lf", &v[0], &v[1], &v[2], &v[3]) == 4 && v[0] > 0 && v[1] > 0 && v[2] > 0 && v[3] > 0)
+      for (int k = 0; k < 4; ++k) ns[k] = v[k];
+  }
   const int64_t cnt[4] = {p->nF, p->n4, p->n2, p->nR};
   double scale = 100.0;
   uint32_t w[4];

@@ -8,6 +8,7 @@ from .cache import (
     PhysicalPageIndex,
     PrecisionPool,
     ThreePrecisionCache,
+    adopt_reference_cache,
     build_three_precision_cache,
     precision_cache_active_storage_breakdown,
     precision_cache_storage_breakdown,
@@ -29,7 +30,7 @@ from .executor import (
 
 __all__ = [
     "CompactInt2ValueArena", "CompactInt4KeyArena", "LayerCompressionPlan", "PackedArenas", "PageClass",
-    "PhysicalPageIndex", "PrecisionPool", "ThreePrecisionCache", "build_three_precision_cache",
+    "PhysicalPageIndex", "PrecisionPool", "ThreePrecisionCache", "adopt_reference_cache", "build_three_precision_cache",
     "precision_cache_active_storage_breakdown", "precision_cache_storage_breakdown",
     "DynamicCacheStats", "append_generated_token", "flush_recent",
     "SplitKExecutor", "SplitKWorkspace", "allocate_splitk_workspace", "allocated_workspace_bytes",

@@ -209,6 +209,77 @@ class PackedArenas:
         g.sm_scale = float(sm_scale)
         return g
 
+    @classmethod
+    def from_reference_cache(cls, cache) -> "PackedArenas":
+        """Adopt, without copying any payload, a cache object built by the reference's own
+        ``build_three_precision_cache`` on a CUDA device (r2omni/sspa/runtime/precision_pool.py:210-274, 787-984):
+        the arenas here are views of the very tensors the reference's executor binds
+        (r2omni/sspa/kernels/triton_fourq_splitk.py:1772-1811, 1833-1907), so a decode through this library reads
+        the reference's bytes in place and a fused append lands in the reference's residual ring.  The object is
+        read by attribute only; nothing of the reference is imported.  Supported: the INT4-key / tiered-value
+        variant with generated values going to the INT2 pool; anything else raises ValueError.  Token bookkeeping
+        arrays (global / logical indices of the packed pools) are copied, they are not payload."""
+        ck = getattr(cache, "compact_key", None)
+        if ck is None or int(getattr(ck, "bit_width", 0)) != 4 or getattr(cache, "matched_fp", False):
+            raise ValueError("only caches with a compact INT4 key arena can be adopted")
+        if getattr(cache, "generated_value_precision", "int2") != "int2":
+            raise ValueError("only caches whose generated values go to the INT2 pool can be adopted")
+        i2 = cache.int2_pool.packed_v
+        if i2 is None or not hasattr(i2, "capacity"):
+            raise ValueError("the INT2-value pool must be a preallocated arena")
+        ring = cache.recent_fp_pool
+        if ring.length_device is None or ring.fp_k is None or ring.capacity <= 0:
+            raise ValueError("the residual ring must be preallocated with a device-side length")
+        dev, dtype = ck.packed.device, ring.fp_k.dtype
+        if dev.type != "cuda":
+            raise RuntimeError("only CUDA-resident caches can be adopted; there is no CPU path")
+        h, d = int(ck.packed.shape[0]), 128
+        n_fp, n_i4 = int(cache.fp_pool.token_count), int(cache.int4_pool.token_count)
+
+        def empty(*shape, dtype):
+            return torch.zeros((1, *shape), device=dev, dtype=dtype)
+
+        fp_v = cache.fp_pool.fp_v.unsqueeze(0) if n_fp else empty(h, 0, d, dtype=dtype)
+        if n_i4:
+            i4 = cache.int4_pool.packed_v
+            i4_packed = i4.packed.view(1, h, n_i4, d // 2)
+            i4_scale = i4.scale.view(1, h, n_i4, 1)
+            if i4_scale.dtype != torch.float32:
+                raise ValueError("INT4-value scales must be float32")
+        else:
+            i4_packed, i4_scale = empty(h, 0, d // 2, dtype=torch.uint8), empty(h, 0, 1, dtype=torch.float32)
+
+        def meta(pool, capacity=None):
+            src = pool.page_index.global_token_indices, pool.page_index.logical_positions
+            n = int(src[0].numel())
+            cap = n if capacity is None else max(int(capacity), n)
+            out = [torch.full((1, cap), -1, device=dev, dtype=torch.long) for _ in src]
+            for o, t in zip(out, src):
+                o[0, :n] = t.to(dev)
+            return out
+
+        i2_active = int(i2.active_length)
+        fp_g, fp_l = meta(cache.fp_pool)
+        i4_g, i4_l = meta(cache.int4_pool)
+        i2_g, i2_l = meta(cache.int2_pool, int(i2.capacity))
+        return cls(
+            dtype=dtype, page_size=int(cache.page_size), k_block=int(ck.superblock_size), v2_group=int(i2.group_size),
+            flush=int(cache.recent_flush_size),
+            k_packed=ck.packed.unsqueeze(0), k_scale=ck.scale.unsqueeze(0), k_zero=ck.zero_point.unsqueeze(0),
+            k_active=int(ck.active_length), k_offsets=tuple(int(v) for v in ck.segment_offsets),
+            fp_v=fp_v, i4_packed=i4_packed, i4_scale=i4_scale,
+            i2_packed=i2.packed.unsqueeze(0), i2_scale=i2.scale.unsqueeze(0), i2_zero=i2.zero_point.unsqueeze(0),
+            i2_active=i2_active,
+            recent_k=ring.fp_k.unsqueeze(0), recent_v=ring.fp_v.unsqueeze(0),
+            recent_len_device=ring.length_device.view(1),
+            recent_global=ring.global_index_buffer.unsqueeze(0), recent_logical=ring.logical_position_buffer.unsqueeze(0),
+            recent_page_lengths=ring.page_index.lengths.unsqueeze(0), recent_len=int(ring.active_length or 0),
+            i2_global=i2_g, i2_logical=i2_l, fp_global=fp_g, fp_logical=fp_l, i4_global=i4_g, i4_logical=i4_l,
+            evicted_global=cache.evicted_global_indices.to(dev).reshape(1, -1).long(),
+            generated_k_offset=int(getattr(cache, "generated_k_offset", 0)) or int(ck.active_length),
+            static_i2_tokens=i2_active,
+        )
+
     def view(self) -> L.CacheView:
         if self._view is None:
             v = L.CacheView()
@@ -431,6 +502,19 @@ class PrecisionPool:
                                  glob[r][:n], logi[r][:n])
 
     @property
+    def payload_bytes(self) -> int:
+        """Allocated payload bytes of the pool, reserved capacity included (precision_pool.py:170-176): what the
+        reference's attention manager sums for its storage statistics."""
+        a, h = self._a, self._a.num_kv_heads
+        if self.name == "fp":
+            return int(h * a.n_fp * 256)
+        if self.name == "int4":
+            return int(h * a.n_i4 * 68)
+        if self.name == "int2":
+            return int(h * a.i2_capacity * (32 + 3 * (128 // a.v2_group)))
+        return int(2 * h * a.recent_capacity * 256)
+
+    @property
     def active_payload_bytes(self) -> int:
         a, n = self._a, self.token_count
         h = a.num_kv_heads
@@ -642,6 +726,12 @@ def build_three_precision_cache(
         pack_v_int2_into(value, i2_t.to(dev), arenas.i2_packed[0], arenas.i2_scale[0], arenas.i2_zero[0],
                          group=arenas.v2_group, dst_start=0)
     return ThreePrecisionCache(arenas)
+
+
+def adopt_reference_cache(cache) -> ThreePrecisionCache:
+    """This library's cache object over the tensors of a cache the reference built (zero copy, see
+    PackedArenas.from_reference_cache): hand it to allocate_splitk_workspace / prepare_splitk_executor as usual."""
+    return ThreePrecisionCache(PackedArenas.from_reference_cache(cache))
 
 
 def stack_arenas(caches) -> PackedArenas:
