@@ -143,10 +143,12 @@ def fwht128(x: torch.Tensor) -> torch.Tensor:
 def qk_mrope(query: torch.Tensor, key: torch.Tensor, cos: torch.Tensor, sin: torch.Tensor, sections,
              apply_hadamard: bool = False):
     """Qwen multimodal RoPE of q [B,Hq,T,128] and k [B,Hkv,T,128] with cos / sin [3,B,T,128], then optionally the
-    Hadamard transform; elementwise restatement of _qwen_qk_mrope_kernel
-    (r2omni/sspa/kernels/triton_qwen_mrope.py:44-124): out[d] = x[d]*cos[axis(d)] + rot(x)[d]*sin[axis(d)],
+    Hadamard transform; restatement of _qwen_qk_mrope_kernel
+    (r2omni/sspa/kernels/triton_qwen_mrope.py:44-212): out[d] = x[d]*cos[axis(d)] + rot(x)[d]*sin[axis(d)],
     rot(x)[d] = -x[d+64] for d < 64 and x[d-64] above, axis by the section of d mod 64, fp32, rounded to the
-    input type.  Parity unpinned: the reference has no CPU form of this kernel to run against."""
+    input type.  The reference's kernel is compiled code: its sum is one rounded product (rot*sin) fused into a
+    multiply-add with the other (x*cos), which is what this computes (the fused step in float64, rounded once more
+    to float32).  Pinned by tests/golden/mrope_reference.npz, which holds that kernel's own outputs."""
     d = torch.arange(128)
     sd = d % 64
     axis = torch.where(sd < sections[0], 0, torch.where(sd < sections[0] + sections[1], 1, 2))
@@ -156,7 +158,7 @@ def qk_mrope(query: torch.Tensor, key: torch.Tensor, cos: torch.Tensor, sin: tor
     for x in (query, key):
         xf = x.float()
         rot = torch.cat((-xf[..., 64:], xf[..., :64]), dim=-1)
-        y = xf * c[:, None] + rot * s[:, None]
+        y = (xf.double() * c[:, None].double() + (rot * s[:, None]).double()).float()
         if apply_hadamard:
             y = fwht128(y)
         outs.append(y.to(x.dtype))

@@ -5,12 +5,13 @@
 // r2omni/sspa/kernels/triton_fourq_splitk.py:449-1020, 1243-1547).
 //
 // Shape of the kernel
-//   * grid = 2 CTAs per SM; every CTA owns a contiguous, byte-balanced range of
-//     the flat tile list (request, kv head, pool, tile) and keeps ONE running
-//     (max, sum-exp, out) state per (request, kv head) it crosses.
-//   * warp 4 is the producer: it streams each tile's key nibbles, key
-//     scale/zero rows and value bytes into a 3-stage shared-memory ring with
-//     1-D bulk copies (TMA) completing on mbarriers.  Warps 0-3 consume.
+//   * grid = one CTA per SM (rounded down to a whole number of CTAs per (request, kv head) when there are at
+//     least two per head); every CTA owns a contiguous range of the flat tile list (request, kv head, pool,
+//     tile), balanced by measured per-tile cost, and keeps ONE running (max, sum-exp, out) state per
+//     (request, kv head) it crosses.
+//   * warp 8 is the producer: one of its lanes streams each tile's key nibbles, key scale/zero rows, value bytes
+//     and value metadata into a 3-stage shared-memory ring with bulk copies (TMA; a swizzled tensor map for
+//     bf16 values) completing on mbarriers.  Warps 0-7 consume, one 32-token key block per warp and tile.
 //   * tokens sit on the M axis of mma.sync.m16n8k16 and the (<= 8) query heads
 //     of the GQA group on N, so no MMA lane is padding:
 //       S^T[tok,head] = K[tok,ch] Q'^T[ch,head],  O^T[dim,head] += V^T[dim,tok] P^T[tok,head].
@@ -18,11 +19,12 @@
 //     or code * 2^-20 straight out of an AND), so a key nibble costs 5/8 of an
 //     ALU instruction.  Per-channel key scales are folded into Q' once per
 //     32-token block as an exact two-term fp16 sum (hi + lo = q * scale), the zero points
-//     become one extra MMA chain per block, per-token INT4-value scales are
+//     are subtracted from the codes with one exact HSUB2 per register, per-token INT4-value scales are
 //     folded into P, INT2 values are dequantised in registers.
-//   * partial states go to a small workspace; the last CTA to finish a
-//     (request, kv head) merges them, writes the output, applies the optional
+//   * partial states go to a small workspace; the last CTA to finish a group of nine partials merges them, the
+//     last group of a (request, kv head) merges the group results, writes the output, applies the optional
 //     Hadamard epilogue and the fused append.
+//   * the residual window is read in 64-token tiles, 16 tokens per warp, two tiles in work at once.
 //
 // Every wait is bounded: a wait that gives up records R2K_ERR_DEVICE_TIMEOUT in
 // the workspace, the warp stops consuming and the kernel still terminates.
@@ -701,7 +703,7 @@ __global__ void __launch_bounds__(kThreads, kCtasPerSm) decode_kernel(const __gr
       if (++stage == kStages) { stage = 0; phase ^= 1u; }
     }
 
-    // ---- this CTA's partial for (b, h): merge the four warps through shared memory ----
+    // ---- this CTA's partial for (b, h): merge the eight warps through shared memory ----
     set_units(st, 0);
 #pragma unroll
     for (int d = 4; d < 32; d <<= 1) {

@@ -362,7 +362,7 @@ __global__ void mrope_rows_kernel(MropeArgs a) {
                              a.rot_dtype);
     const float s = load_rot(a.sin, axis * a.sin_stride[0] + request * a.sin_stride[1] + token * a.sin_stride[2] + d * a.sin_stride[3],
                              a.rot_dtype);
-    r[e] = __fadd_rn(__fmul_rn(x[e], c), __fmul_rn(rotated, s));
+    r[e] = __fmaf_rn(x[e], c, __fmul_rn(rotated, s));   // the reference's compiled form of x*cos + rot*sin: one product rounded, one fused
   }
   if (a.hadamard) {
     const float p = __fadd_rn(r[0], r[1]), m = __fsub_rn(r[0], r[1]), c = __fadd_rn(r[2], r[3]), d = __fsub_rn(r[2], r[3]);

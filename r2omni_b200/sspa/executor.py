@@ -165,6 +165,15 @@ class SplitKExecutor:
         if isinstance(global_index, int) and isinstance(logical_position, int):
             ap.indices, ap.global_index, ap.logical_position = None, global_index, logical_position
             self._idx = None
+        elif logical_position is None:
+            # a ready device table [B,2] of (global index, logical position): read by the launch in place, so a
+            # caller that replays captured steps only has to advance it on the stream
+            t = global_index
+            if (not torch.is_tensor(t) or t.dtype != torch.int64 or tuple(t.shape) != (a.batch, 2) or t.device != query.device
+                    or not t.is_contiguous()):
+                raise ValueError("append index table must be a contiguous int64 [B,2] tensor on the cache device")
+            self._idx = t
+            ap.indices, ap.global_index, ap.logical_position = t.data_ptr(), 0, 0
         else:
             cols = []
             for value in (global_index, logical_position):

@@ -65,9 +65,11 @@ int main() {
     }
     ++cases;
   }
-  // the benchmark geometries
-  if (check(16, 128, 128, 65, 4, 296, 18, 27, 30, 9) || check(2, 0, 4096, 4097, 4, 296, 18, 27, 30, 9) ||
-      check(64, 256, 256, 129, 4, 296, 18, 27, 30, 9) || check(4, 0, 32, 0, 4, 144, 18, 27, 30, 9))
+  // the benchmark geometries (tiles of 128 bf16-value / 256 INT4- or INT2-value / 64 residual tokens; grids of one
+  // CTA per SM, rounded down to a whole number of CTAs per (request, kv head)): 8 x 32768 tokens on 2 kv heads,
+  // 1M tokens of one request, 16 x 65536 tokens on 4 kv heads, 4096 INT4-value tokens of one request
+  if (check(16, 64, 64, 33, 2, 144, 14, 21, 24, 5) || check(2, 0, 2048, 2049, 2, 148, 14, 21, 24, 5) ||
+      check(64, 128, 128, 65, 2, 128, 14, 21, 24, 5) || check(2, 0, 16, 0, 2, 36, 14, 21, 24, 5))
     return 2;
   std::printf("OK %ld cases\n", cases + 4);
   return 0;

@@ -1,6 +1,6 @@
-"""Qwen multimodal RoPE (+ Hadamard) prologue kernel against the oracle's elementwise restatement of
-_qwen_qk_mrope_kernel (r2omni/sspa/kernels/triton_qwen_mrope.py:44-124).  The kernel rounds the two products
-and their sum separately, as the elementwise form does, so the rounded result is bit-exact."""
+"""Qwen multimodal RoPE (+ Hadamard) prologue kernel against the oracle's restatement of _qwen_qk_mrope_kernel
+(r2omni/sspa/kernels/triton_qwen_mrope.py:44-212), which is itself pinned by outputs of the reference's kernel
+(tests/golden/mrope_reference.npz), and against those outputs directly: bit-exact."""
 import pytest
 import torch
 
@@ -51,3 +51,16 @@ def test_mrope_strided_tables_in_place_output_and_errors():
         R.qwen_qk_mrope(qd, kd, cos.cuda()[:2], sin.cuda()[:2], (16, 24, 24))
     with pytest.raises(RuntimeError):
         R.qwen_qk_mrope(q, k, cos, sin, (16, 24, 24))
+
+
+def test_mrope_matches_the_reference_kernel_fixture():
+    import os
+
+    import numpy as np
+    from make_mrope_golden import CASES, SECTIONS, mrope_inputs
+    z = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "mrope_reference.npz"))
+    for name, batch, hq, hkv, tokens, dtype, rot_dtype, hadamard in CASES:
+        q, k, cos, sin = mrope_inputs(name, batch, hq, hkv, tokens, dtype, rot_dtype)
+        got_q, got_k = R.qwen_qk_mrope(q.cuda(), k.cuda(), cos.cuda(), sin.cuda(), SECTIONS, apply_hadamard=hadamard)
+        assert np.array_equal(got_q.cpu().view(torch.int16).numpy(), z[name + "_q"]), name
+        assert np.array_equal(got_k.cpu().view(torch.int16).numpy(), z[name + "_k"]), name

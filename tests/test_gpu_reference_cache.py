@@ -76,3 +76,21 @@ def test_reference_triton_decoder_agrees_on_the_same_cache(ref):
     ours = make_executor(R.adopt_reference_cache(cache), 16)(queries[0].cuda()).float()
     # both are bf16 outputs of the same cache: one bf16 ulp of slack on top of the attention tolerance
     assert_close(ours, theirs, "this library against the reference's Triton decoder")
+
+
+@pytest.mark.parametrize("hadamard", [False, True])
+@pytest.mark.parametrize("rot_dtype", [torch.bfloat16, torch.float32])
+def test_mrope_prologue_against_the_reference_kernel(ref, hadamard, rot_dtype):
+    """The reference's fused multimodal-RoPE kernel (Triton, run here on the GPU) and this library's give the same
+    bits (the library computes x*cos + rot*sin as the reference's compiled kernel does: one product rounded, the
+    other fused into the addition)."""
+    from r2omni.sspa.kernels.triton_qwen_mrope import qwen_qk_mrope as reference_mrope
+    g = torch.Generator().manual_seed(17)
+    q = torch.randn(8, 16, 1, 128, generator=g).to(torch.bfloat16).cuda()
+    k = torch.randn(8, 2, 1, 128, generator=g).to(torch.bfloat16).cuda()
+    angle = torch.rand(3, 8, 1, 128, generator=g) * 6.2831853
+    cos, sin = torch.cos(angle).to(rot_dtype).cuda(), torch.sin(angle).to(rot_dtype).cuda()
+    want_q, want_k = reference_mrope(q, k, cos, sin, [16, 24, 24], apply_hadamard=hadamard)
+    got_q, got_k = R.qwen_qk_mrope(q, k, cos, sin, (16, 24, 24), apply_hadamard=hadamard)
+    assert torch.equal(got_q.view(torch.int16), want_q.view(torch.int16))
+    assert torch.equal(got_k.view(torch.int16), want_k.view(torch.int16))

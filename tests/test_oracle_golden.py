@@ -71,3 +71,20 @@ def test_chunked_state_equals_whole_pool_state():
 def test_fwht_is_orthonormal_involution():
     x = torch.randn(5, 128, generator=torch.Generator().manual_seed(0))
     assert torch.allclose(O.fwht128(O.fwht128(x)), x, atol=1e-5)
+
+
+def test_oracle_mrope_reproduces_the_reference_kernel_outputs():
+    """tests/golden/mrope_reference.npz holds the outputs of the reference's own multimodal-RoPE kernel (made on a
+    GPU by tests/golden/make_mrope_golden.py): the oracle must give the same 16-bit patterns."""
+    import os
+
+    import numpy as np
+    from make_mrope_golden import CASES, SECTIONS, mrope_inputs
+    from recipe import digest
+    z = np.load(os.path.join(os.path.dirname(os.path.abspath(__file__)), "golden", "mrope_reference.npz"))
+    for name, batch, hq, hkv, tokens, dtype, rot_dtype, hadamard in CASES:
+        q, k, cos, sin = mrope_inputs(name, batch, hq, hkv, tokens, dtype, rot_dtype)
+        assert digest(q, k, cos.float(), sin.float()) == str(z[name + "_digest"]), name
+        got_q, got_k = O.qk_mrope(q, k, cos, sin, SECTIONS, hadamard)
+        assert np.array_equal(got_q.contiguous().view(torch.int16).numpy(), z[name + "_q"]), name
+        assert np.array_equal(got_k.contiguous().view(torch.int16).numpy(), z[name + "_k"]), name
