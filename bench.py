@@ -16,6 +16,10 @@ Workloads (``config.workload``):
   above (~21.8 GB resident).  A step is the attention of ALL layers: 28 decode launches with fused append, joined by
   programmatic dependent launch; every 128 steps all layers flush.
 
+* ``thinker_3b_b32``: greedy decode of a random-weight 36-layer Qwen2.5-Omni-3B-shaped decoder (hidden 2048, MLP
+  11008, vocabulary 151936), batch 32, 16384 prefilled tokens per request and layer, 256 generated tokens, with this
+  library's attention manager path in every layer; its line reports tokens/s.
+
 ``value`` is the whole-job algorithmic GB/s with inputs resident in HBM (CUDA-graph replays, device-timed); ``e2e``
 is the same metric through the public operator call with host query/key/value buffers and a host read of the output
 inside the timed region.  After the timed regions one decode of the benchmarked caches is compared with the CPU
@@ -840,13 +844,224 @@ def triton_reference_record(device, bench, steps=200, sets=3):
         return {"error": repr(exc)[:400], "where": traceback.format_exc().strip().splitlines()[-3:]}
 
 
+# --------------------------------------------------------------------------- #
+# greedy decode of a random-weight thinker with the packed-KV attention in the loop
+# --------------------------------------------------------------------------- #
+THINKER = dict(layers=36, hidden=2048, hq=16, hkv=2, mlp=11008, vocab=151936, theta=1.0e6, batch=32, tokens=16384,
+               new_tokens=256, page=64, mix=(0.25, 0.5))
+
+
+class SyntheticThinker:
+    """A Qwen2.5-Omni-3B-shaped text decoder with random weights (~N(0, 0.02), bf16): RMSNorm, q/k/v projections
+    with bias, multimodal RoPE (text positions: the three axes agree), packed-KV attention through
+    PackedKVAttentionManager (kernel_backend "cuda_sm100"), output projection, SwiGLU MLP; final norm, LM head,
+    argmax.  Every layer's cache holds `tokens` prefilled tokens per request, packed from random bf16
+    activations with seeded page precisions.  One decode step is captured into a CUDA graph: token ids,
+    positions and append indices live on the device and are advanced inside the graph."""
+
+    def __init__(self, device, cfg):
+        import types
+
+        import r2omni_b200 as R
+        from gpu_helpers import make_plan
+        self.R, self.device, self.cfg = R, device, cfg
+        c = cfg
+        g = torch.Generator(device=device).manual_seed(1234)
+        def w(*shape):
+            return (torch.randn(*shape, generator=g, device=device) * 0.02).to(torch.bfloat16)
+        def linear(n_in, n_out, bias):
+            layer = torch.nn.Linear(n_in, n_out, bias=bias, device=device, dtype=torch.bfloat16)
+            with torch.no_grad():
+                layer.weight.copy_(w(n_out, n_in))
+                if bias:
+                    layer.bias.copy_(w(n_out))
+            return layer
+        self.embed, self.lm_head = w(c["vocab"], c["hidden"]), w(c["vocab"], c["hidden"])
+        self.final_norm = torch.ones(c["hidden"], device=device, dtype=torch.bfloat16)
+        self.manager = R.PackedKVAttentionManager(num_query_heads=c["hq"], mrope_section=(16, 24, 24), device_positions=True)
+        self.layers = []
+        t_build = time.perf_counter()
+        for l in range(c["layers"]):
+            attn = types.SimpleNamespace(
+                head_dim=128, q_proj=linear(c["hidden"], c["hq"] * 128, True), k_proj=linear(c["hidden"], c["hkv"] * 128, True),
+                v_proj=linear(c["hidden"], c["hkv"] * 128, True), o_proj=linear(c["hq"] * 128, c["hidden"], False))
+            self.layers.append(types.SimpleNamespace(
+                attn=attn, ln1=torch.ones(c["hidden"], device=device, dtype=torch.bfloat16),
+                ln2=torch.ones(c["hidden"], device=device, dtype=torch.bfloat16),
+                gate=linear(c["hidden"], c["mlp"], False), up=linear(c["hidden"], c["mlp"], False),
+                down=linear(c["mlp"], c["hidden"], False)))
+            classes = page_classes(c["tokens"] // c["page"], 300 + l, c["mix"][0], c["mix"][1])
+            caches = []
+            for b in range(c["batch"]):
+                key, value = synth_kv(c["tokens"], (300 + l) * 1000 + b, device, hkv=c["hkv"])
+                caches.append(R.build_three_precision_cache(
+                    key, value, make_plan(classes, c["page"], RING), page_size=c["page"], key_quantization_superblock=K_BLOCK,
+                    int2_group_size=V2_GROUP, compact_key_append_capacity=RING * (c["new_tokens"] // RING + 2),
+                    recent_flush_size=RING))
+                del key, value
+            self.manager.adopt_layer(l, caches, c["tokens"])
+            del caches
+        self.build_seconds = time.perf_counter() - t_build
+        B = c["batch"]
+        self.inv_freq = 1.0 / (c["theta"] ** (torch.arange(0, 128, 2, device=device, dtype=torch.float32) / 128.0))
+        self.tok = torch.randint(0, c["vocab"], (B,), generator=g, device=device)
+        self.pos = torch.full((B,), float(c["tokens"]), device=device, dtype=torch.float32)
+        self.idx = torch.full((B, 2), c["tokens"], device=device, dtype=torch.int64)
+        self.graphs, self.phase = [], 0
+
+    def _step(self):
+        """One decode step on the current stream; advances tok / pos / idx on the device."""
+        c, F = self.cfg, torch.nn.functional
+        B = c["batch"]
+        x = self.embed[self.tok].view(B, 1, c["hidden"])
+        angle = self.pos[:, None] * self.inv_freq[None, :]
+        emb = torch.cat((angle, angle), dim=-1)                       # [B,128]
+        cos = emb.cos().view(1, B, 1, 128).expand(3, B, 1, 128)
+        sin = emb.sin().view(1, B, 1, 128).expand(3, B, 1, 128)
+        for l, layer in enumerate(self.layers):
+            h = F.rms_norm(x, (c["hidden"],), layer.ln1, 1e-6)
+            x = x + self.manager.active_forward(l, layer.attn, h, (cos, sin), append_indices=self.idx)
+            h = F.rms_norm(x, (c["hidden"],), layer.ln2, 1e-6)
+            x = x + layer.down(F.silu(layer.gate(h)) * layer.up(h))
+        h = F.rms_norm(x, (c["hidden"],), self.final_norm, 1e-6)
+        logits = h.view(B, c["hidden"]) @ self.lm_head.t()
+        self.tok.copy_(logits.argmax(dim=-1))
+        self.pos.add_(1.0)
+        self.idx.add_(1)
+
+    def _host_mirrors(self):
+        return [(s.original_seq_len, s.append_count, s.last_cache_position, s.calls, s.kernel_calls,
+                 s.dynamic_stats.appended_tokens, s.fourq_executor.arenas.recent_len) for s in self.manager._states.values()]
+
+    def capture(self, phases):
+        """Capture one decode step per cache geometry: the launch geometry is part of a captured graph, and every
+        flush moves 128 tokens per request from the residual window into the INT2-value pool, so phase k (after k
+        flushes) gets its own graph, captured ahead of time with the pool extents it will have.  The host-side
+        bookkeeping a step does runs once per capture and is undone; `advance` redoes it after every replay."""
+        for _ in range(2):      # eager steps first: library handles, workspaces
+            self.flush_if_needed()
+            self._step()
+        torch.cuda.synchronize(self.device)
+        self.flush_if_needed()
+        self.graphs, self.phase = [], 0
+        arenas = [s.fourq_executor.arenas for s in self.manager._states.values()]
+        base = [(a.k_active, a.i2_active) for a in arenas]
+        for k in range(phases):
+            before = self._host_mirrors()
+            for a, (ka, ia) in zip(arenas, base):
+                a.k_active, a.i2_active = ka + RING * k, ia + RING * k
+            graph = torch.cuda.CUDAGraph()
+            with torch.cuda.graph(graph):
+                self._step()
+            self.graphs.append(graph)
+            for s, m in zip(self.manager._states.values(), before):
+                (s.original_seq_len, s.append_count, s.last_cache_position, s.calls, s.kernel_calls,
+                 s.dynamic_stats.appended_tokens, s.fourq_executor.arenas.recent_len) = m
+        for a, (ka, ia) in zip(arenas, base):
+            a.k_active, a.i2_active = ka, ia
+
+    def advance(self):
+        for s in self.manager._states.values():
+            s.last_cache_position = s.original_seq_len
+            s.original_seq_len += 1
+            s.append_count += 1
+            s.calls += 1
+            s.kernel_calls += 1
+            s.dynamic_stats.appended_tokens += 1
+            s.fourq_executor.arenas.recent_len += 1
+
+    def flush_if_needed(self):
+        return sum(1 for l in range(len(self.layers)) if self.manager.flush_if_full(l))
+
+    def generate(self, steps, host_loop=False, host_tok=None):
+        """`steps` replays of the captured step (flushes of full residual windows in between).  host_loop: the token
+        ids go through pinned host memory every step, as a serving loop with a host-side sampler / stop check does."""
+        flushes = 0
+        for _ in range(steps):
+            flushed = self.flush_if_needed()
+            if flushed:
+                flushes += flushed
+                self.phase += 1
+            if host_loop:
+                self.tok.copy_(host_tok, non_blocking=True)
+            self.graphs[self.phase].replay()
+            self.advance()
+            if host_loop:
+                host_tok.copy_(self.tok, non_blocking=True)
+                torch.cuda.current_stream(self.device).synchronize()
+        return flushes
+
+
+def run_thinker(args):
+    import torch.distributed as dist
+    rank, world = int(os.environ.get("RANK", "0")), int(os.environ.get("WORLD_SIZE", "1"))
+    local = int(os.environ.get("LOCAL_RANK", "0"))
+    device = torch.device("cuda", local)
+    torch.cuda.set_device(device)
+    dist_on = world > 1
+    if dist_on:
+        dist.init_process_group("nccl", device_id=device)
+    from r2omni_b200 import _lib as L
+    L.lib()
+    cfg = dict(THINKER)
+    steps = args.steps if args.steps else cfg["new_tokens"]
+    model = SyntheticThinker(device, cfg)
+    warm = max(3, min(args.warmup, 8))
+    model.capture(phases=(warm + steps + min(steps, 64) + 4) // RING + 2)
+    model.generate(warm)
+    with ClockSampler(local) as clocks:
+        ms, flushes = time_region(device, lambda: model.generate(steps), dist_on)
+    tokens_per_s = cfg["batch"] * steps * world / (ms * 1e-3)
+    host_tok = torch.empty(cfg["batch"], dtype=torch.int64).pin_memory()
+    host_tok.copy_(model.tok)
+    e_steps = min(steps, 64)
+    e_ms, _ = time_region(device, lambda: model.generate(e_steps, host_loop=True, host_tok=host_tok), dist_on)
+    a = model.manager._states[0].fourq_executor.arenas
+    kv_bytes = cfg["layers"] * algorithmic_bytes(a.n_fp, a.n_i4, a.i2_active, RING // 2, cfg["batch"], cfg["hq"], cfg["hkv"], True)
+    per_layer = cfg["hidden"] * (cfg["hq"] + 2 * cfg["hkv"]) * 128 + cfg["hq"] * 128 * cfg["hidden"] + 3 * cfg["hidden"] * cfg["mlp"]
+    weight_bytes = 2 * (cfg["layers"] * per_layer + cfg["vocab"] * cfg["hidden"])
+    peak, peak_kind = measured_peak_gbs()
+    if rank == 0:
+        line = {
+            "metric": "greedy_decode_tokens_per_s", "value": round(tokens_per_s, 1), "unit": "tokens/s", "n_gpus": world,
+            "steps": steps, "warmup": warm, "ms_per_step": round(ms / steps, 4), "higher_is_better": True, "scaling": "weak",
+            "vs_baseline": None, "dtype": "bf16 weights and activations; packed INT4 keys, bf16/INT4/INT2 value pages",
+            "data": "synthetic",
+            "config": {"workload": "thinker_3b_b32", "layers": cfg["layers"], "hidden": cfg["hidden"], "heads": "16q/2kv x128",
+                       "mlp": cfg["mlp"], "vocab": cfg["vocab"], "rope_theta": cfg["theta"], "batch_per_gpu": cfg["batch"],
+                       "prefilled_tokens": cfg["tokens"], "generated_tokens": steps,
+                       "pages": "64 tokens; bf16/INT4/INT2 = 25,50,25 % from a seed", "weights": "random ~N(0, 0.02), bf16",
+                       "attention": "PackedKVAttentionManager, kernel_backend cuda_sm100: fused mRoPE launch + one decode launch "
+                                    "with fused append per layer; flush of all layers every 128 steps",
+                       "step": "one CUDA-graph replay (36 layers, LM head, argmax); token ids, positions and append "
+                               "indices advance on the device", "l2": "7 GB of caches + 6.7 GB of weights per step (larger than L2)",
+                       "parallelism": f"{world} independent replicas" if world > 1 else "1 GPU"},
+            "gpu_launches": int(steps * cfg["layers"] * 2 + flushes * 3),
+            "flushes_in_region": int(flushes),
+            "roofline": {"bound": "hbm", "kernel": "whole decode step (attention + GEMV-like projections)",
+                         "achieved": round((kv_bytes + weight_bytes) / (ms / steps * 1e-3) / 1e9, 1), "peak": peak,
+                         "peak_source": peak_kind, "unit": "GB/s",
+                         "frac": round((kv_bytes + weight_bytes) / (ms / steps * 1e-3) / 1e9 / peak, 4),
+                         "bytes_per_step": {"packed_kv": int(kv_bytes), "weights": int(weight_bytes)}, "traffic": None},
+            "e2e": {"value": round(cfg["batch"] * e_steps * world / (e_ms * 1e-3), 1), "unit": "tokens/s",
+                    "ms_per_step": round(e_ms / e_steps, 4), "steps": e_steps,
+                    "h2d_bytes_per_step": cfg["batch"] * 8, "d2h_bytes_per_step": cfg["batch"] * 8,
+                    "call": "token ids from pinned host memory in, graph replay, sampled ids back to the host, stream wait"},
+            "build_seconds": round(model.build_seconds, 1), "clocks": clocks.summary(),
+            "stats_layer0": model.manager.get_stats()[0],
+        }
+        print(json.dumps(line))
+    if dist_on:
+        dist.destroy_process_group()
+
+
 def main():
     ap = argparse.ArgumentParser()
     ap.add_argument("--gpus", type=int, default=1)
     ap.add_argument("--steps", type=int, default=None)
     ap.add_argument("--warmup", type=int, default=16)
     ap.add_argument("--impl", default="ours", choices=["ours", "reference"])
-    ap.add_argument("--workload", default="decode_32k_b8", choices=sorted(WORKLOADS))
+    ap.add_argument("--workload", default="decode_32k_b8", choices=sorted(WORKLOADS) + ["thinker_3b_b32"])
     ap.add_argument("--no-cpu-baseline", action="store_true")
     ap.add_argument("--no-sharded", action="store_true")
     ap.add_argument("--no-e2e", action="store_true")
@@ -854,6 +1069,12 @@ def main():
     ap.add_argument("--no-triton-reference", action="store_true")
     ap.add_argument("--page-mix", default=None, help="percent of bf16,INT4,INT2 value pages (kernel studies)")
     args = ap.parse_args()
+    if args.workload == "thinker_3b_b32":
+        if args.impl == "reference":
+            args.workload = "decode_32k_b8"      # the CPU arm times the attention path, whatever drives it
+        else:
+            run_thinker(args)
+            return
     w = dict(WORKLOADS[args.workload])
     if args.steps is None:
         args.steps = {"decode_7b_28l": 256, "decode_4k_b1": 16384}.get(args.workload, 8192)
