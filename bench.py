@@ -16,6 +16,8 @@ Workloads (``config.workload``):
   above (~21.8 GB resident).  A step is the attention of ALL layers: 28 decode launches with fused append, joined by
   programmatic dependent launch; every 128 steps all layers flush.
 
+* ``decode_3b_36l``: the attention of the thinker workload below alone: 36 layers of 16 query / 2 KV heads, batch 32,
+  16384 tokens per request (~7.6 GB resident); a step is 36 decode launches.
 * ``thinker_3b_b32``: greedy decode of a random-weight 36-layer Qwen2.5-Omni-3B-shaped decoder (hidden 2048, MLP
   11008, vocabulary 151936), batch 32, 16384 prefilled tokens per request and layer, 256 generated tokens, with this
   library's attention manager path in every layer; its line reports tokens/s.
@@ -55,6 +57,7 @@ WORKLOADS = {
     "decode_32k_b8": dict(hq=16, hkv=2, batch=8, tokens=32768, sets=4, page=64, mix=(0.25, 0.5), step="launch", append=True),
     "decode_4k_b1": dict(hq=16, hkv=2, batch=1, tokens=4096, sets=128, page=32, mix=(0.0, 1.0), step="launch", append=False),
     "decode_7b_28l": dict(hq=28, hkv=4, batch=16, tokens=65536, sets=28, page=64, mix=(0.25, 0.5), step="round", append=True),
+    "decode_3b_36l": dict(hq=16, hkv=2, batch=32, tokens=16384, sets=36, page=64, mix=(0.25, 0.5), step="round", append=True),
     "small": dict(hq=16, hkv=2, batch=2, tokens=4096, sets=4, page=64, mix=(0.25, 0.5), step="launch", append=True),
 }
 
@@ -1077,7 +1080,7 @@ def main():
             return
     w = dict(WORKLOADS[args.workload])
     if args.steps is None:
-        args.steps = {"decode_7b_28l": 256, "decode_4k_b1": 16384}.get(args.workload, 8192)
+        args.steps = {"decode_7b_28l": 256, "decode_3b_36l": 256, "decode_4k_b1": 16384}.get(args.workload, 8192)
     if args.page_mix is not None:
         mix = [float(x) / 100.0 for x in args.page_mix.split(",")]
         w["mix"] = (mix[0], mix[1])

@@ -331,6 +331,10 @@ __device__ __forceinline__ float load_rot(const void* base, int64_t index, int d
 
 template <bool BF16>
 __global__ void mrope_rows_kernel(MropeArgs a) {
+  // The decode launch that follows on the stream may start its CTAs and prefetch pool tiles right away (it is
+  // launched with programmatic stream serialization); it reads the rows written here only after its own
+  // dependency wait, i.e. after this grid has completed.
+  launch_dependents();
   const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
   const int heads = a.hq + a.hkv;
