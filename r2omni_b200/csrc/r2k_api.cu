@@ -140,6 +140,16 @@ int derive(const R2KGeom* g, DecodeParams* p) {
     const int rounded = p->grid / p->bh_total * p->bh_total;
     if (rounded * 20 >= p->grid * 19) p->grid = rounded;
   }
+  // More than kMergeGroup CTAs on a (request, kv head) pay a second merge level (a store, a ticket and one more
+  // round of loads: ~2.6 us).  A head with so few tiles that kMergeGroup CTAs stream them in less extra time than
+  // that gets kMergeGroup CTAs: measured 11.3 -> 10.0 us per launch for one request x 2 kv heads x 4096 tokens
+  // (18 -> 9 CTAs per head).  The tile weights include fixed costs (about 1.5x the streaming time), hence 3 us.
+  if (p->grid > kMergeGroup * p->bh_total) {
+    double head_ns = 0.0;
+    for (int k = 0; k < 4; ++k) head_ns += (double)cnt[k] * ns[k];
+    const double per_head = (double)p->grid / p->bh_total;
+    if (head_ns / kMergeGroup - head_ns / per_head < 3000.0) p->grid = kMergeGroup * p->bh_total;
+  }
   if ((int64_t)p->grid * p->bh_total >= (int64_t)1 << 31) return R2K_ERR_GEOMETRY;
   p->parts_cap = (p->grid + p->bh_total - 1) / p->bh_total + 1;
   p->groups_cap = (p->parts_cap + kMergeGroup - 1) / kMergeGroup;

@@ -69,7 +69,7 @@ int main() {
   // CTA per SM, rounded down to a whole number of CTAs per (request, kv head)): 8 x 32768 tokens on 2 kv heads,
   // 1M tokens of one request, 16 x 65536 tokens on 4 kv heads, 4096 INT4-value tokens of one request
   if (check(16, 64, 64, 33, 2, 144, 14, 21, 24, 5) || check(2, 0, 2048, 2049, 2, 148, 14, 21, 24, 5) ||
-      check(64, 128, 128, 65, 2, 128, 14, 21, 24, 5) || check(2, 0, 16, 0, 2, 36, 14, 21, 24, 5))
+      check(64, 128, 128, 65, 2, 128, 14, 21, 24, 5) || check(2, 0, 16, 0, 2, 18, 14, 21, 24, 5))
     return 2;
   std::printf("OK %ld cases\n", cases + 4);
   return 0;
