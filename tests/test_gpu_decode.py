@@ -201,7 +201,8 @@ def test_sharded_states_merge_to_the_single_cache_result():
     top, den, acc = O.decode_state(queries[0].float(), O.build_cache(key[:, :1024].contiguous(), value[:, :1024].contiguous(),
                                                                       classes[:16], page_size=64))
     s0 = states[0].cpu()
-    assert torch.allclose(s0[..., 0], top, atol=2e-3)
+    # the state's reference point need not be the true maximum (it moves lazily); its log-sum-exp is what is defined
+    assert torch.allclose(s0[..., 0] + torch.log(s0[..., 1]), top + torch.log(den), atol=2e-3)
     assert_close(s0[..., 2:] / s0[..., 1:2], acc / den.unsqueeze(-1), "shard-0 state")
 
 
