@@ -15,18 +15,13 @@ constexpr int kConsumers = kNW * 32;
 constexpr int kTQ = kNW * 32;               // tokens per tile: INT4-/INT2-value pools (one key block per warp)
 constexpr int kTF = kNW * 16;               // tokens per tile: bf16-value pool
 constexpr int kTR = (kNW / 2) * 16;         // tokens per tile: residual window (16 per warp of one half of the warps)
-constexpr int kStages = 3;
+constexpr int kStages = 4;
 constexpr int kCtasPerSm = 1;
 
-// shared-memory stage: [value region | key payload | key scales | key zeros]
+// Shared-memory stage: [value region | key payload | key scales | key zeros].  The value region of a pool is as
+// large as that pool needs (bf16 values: kTF rows of 256 bytes; INT4 / INT2 values: kTQ rows of 64 bytes + scales),
+// and the key rows follow it directly, so that a stage is no larger than its largest tile and four of them fit.
 constexpr int kOffV = 0;
-constexpr int kVBytes = kTF * 256;
-constexpr int kOffK = kOffV + kVBytes;
-constexpr int kOffKS = kOffK + kTQ * 64;
-constexpr int kOffKZ = kOffKS + (kTQ / 32) * 256;
-constexpr int kStageBytes = kOffKZ + (kTQ / 32) * 128;
-static_assert(kStageBytes % 128 == 0, "stage must stay 128-byte aligned");
-static_assert(kTF % 128 == 0 && kTQ % 128 == 0, "tile windows must start on multiples of the largest key block");
 // value region, per pool
 // bf16-value tiles are stored as two half boxes (channels 0-63, 64-127) of kTF rows x 128 bytes; inside every
 // row the 16-byte chunks are XOR-swizzled by (row & 7) -- the layout of a 128-byte-swizzled tensor copy.
@@ -35,7 +30,19 @@ constexpr int kOffI4Scale = kTQ * 64;            // f32 per token after the nibb
 constexpr int kOffI2Scale = kTQ * 32;            // f16 x groups per token after the crumb rows
 constexpr int kOffI2Zero = kOffI2Scale + kTQ * 8;
 constexpr int kOffRecentV = kTR * 256;           // residual tile: K rows then V rows
-static_assert(kTF * 256 <= kVBytes && kOffI2Zero + kTQ * 4 <= kVBytes && 2 * kTR * 256 <= kVBytes, "value region");
+constexpr int kVBytesFp = kTF * 256;
+constexpr int kVBytesPacked = kTQ * 68;
+static_assert(kOffI2Zero + kTQ * 4 <= kVBytesPacked && kOffI4Scale + kTQ * 4 <= kVBytesPacked, "value region");
+__host__ __device__ constexpr int tile_tokens(int pool) { return pool == 0 ? kTF : kTQ; }
+__host__ __device__ constexpr int off_k(int pool) { return pool == 0 ? kVBytesFp : kVBytesPacked; }       // key nibble rows
+__host__ __device__ constexpr int off_ks(int pool) { return off_k(pool) + tile_tokens(pool) * 64; }          // key scales
+__host__ __device__ constexpr int off_kz(int pool) { return off_ks(pool) + (tile_tokens(pool) / 32) * 256; }  // key zeros
+__host__ __device__ constexpr int stage_end(int pool) { return off_kz(pool) + (tile_tokens(pool) / 32) * 128; }
+constexpr int kStageBytes = ((stage_end(0) > stage_end(1) ? stage_end(0) : stage_end(1)) + 1023) / 1024 * 1024;
+static_assert(kStageBytes % 1024 == 0, "the swizzled value boxes want 1024-byte alignment");
+static_assert(off_k(0) % 128 == 0 && off_k(1) % 128 == 0, "bulk copies want 16-byte aligned destinations");
+static_assert(2 * kTR * 256 <= kStageBytes, "residual tile: key rows and value rows");
+static_assert(kTF % 128 == 0 && kTQ % 128 == 0, "tile windows must start on multiples of the largest key block");
 
 constexpr int kRowFloats = 132;                  // (max, sum, pad, pad, out[128]) per head
 constexpr int kSlotFloats = 8 * kRowFloats;      // one partial: 8 heads of a KV group

@@ -10,7 +10,7 @@
 //     tile), balanced by measured per-tile cost, and keeps ONE running (max, sum-exp, out) state per
 //     (request, kv head) it crosses.
 //   * warp 8 is the producer: one of its lanes streams each tile's key nibbles, key scale/zero rows, value bytes
-//     and value metadata into a 3-stage shared-memory ring with bulk copies (TMA; a swizzled tensor map for
+//     and value metadata into a 4-stage shared-memory ring with bulk copies (TMA; a swizzled tensor map for
 //     bf16 values) completing on mbarriers.  Warps 0-7 consume, one 32-token key block per warp and tile.
 //   * tokens sit on the M axis of mma.sync.m16n8k16 and the (<= 8) query heads
 //     of the GQA group on N, so no MMA lane is padding:
@@ -125,13 +125,13 @@ __device__ __forceinline__ void produce_tile(const DecodeParams& p, const Tile& 
     const int len = tl.pool == 0 ? kTF : kTQ;
     // keys: the whole window, clipped to the arena (its capacity is a multiple of 128 rows, not of the tile)
     const int krows = min(len, p.g.k_capacity - tl.win);
-    copy_piece(stage + kOffK, v.k_packed + (size_t)b * v.k_packed_bstride + ((size_t)h * p.g.k_capacity + tl.win) * 64,
+    copy_piece(stage + off_k(tl.pool), v.k_packed + (size_t)b * v.k_packed_bstride + ((size_t)h * p.g.k_capacity + tl.win) * 64,
                krows * 64, bar, lane, tx);
     const int blk0 = tl.win >> p.kblock_shift;
     const int nblk = min(max(1, len >> p.kblock_shift), (p.g.k_capacity >> p.kblock_shift) - blk0);
     const size_t meta = (size_t)h * (p.g.k_capacity >> p.kblock_shift) + blk0;
-    copy_piece(stage + kOffKS, (const uint8_t*)v.k_scale + (size_t)b * v.k_scale_bstride + meta * 256, nblk * 256, bar, lane, tx);
-    copy_piece(stage + kOffKZ, v.k_zero + (size_t)b * v.k_zero_bstride + meta * 128, nblk * 128, bar, lane, tx);
+    copy_piece(stage + off_ks(tl.pool), (const uint8_t*)v.k_scale + (size_t)b * v.k_scale_bstride + meta * 256, nblk * 256, bar, lane, tx);
+    copy_piece(stage + off_kz(tl.pool), v.k_zero + (size_t)b * v.k_zero_bstride + meta * 128, nblk * 128, bar, lane, tx);
     // values: only rows of this pool; rows of the window outside it are cleared
     uint8_t* vreg = stage + kOffV;
     if (tl.pool == 0) {
@@ -203,9 +203,9 @@ __device__ __forceinline__ void produce_full_tile(const DecodeParams& p, const T
   uint32_t tx = (uint32_t)(len * 64 + nblk * 384);
   tx += pool == 0 ? (uint32_t)(len * 256) : pool == 1 ? (uint32_t)(len * 68) : (uint32_t)(len * 44);
   mbar_arrive_expect_tx(bar, tx);
-  bulk_g2s(stage + kOffK, src.kp + (size_t)win * 64, (uint32_t)(len * 64), bar);
-  bulk_g2s(stage + kOffKS, src.ks + (size_t)blk0 * 256, (uint32_t)(nblk * 256), bar);
-  bulk_g2s(stage + kOffKZ, src.kz + (size_t)blk0 * 128, (uint32_t)(nblk * 128), bar);
+  bulk_g2s(stage + off_k(pool), src.kp + (size_t)win * 64, (uint32_t)(len * 64), bar);
+  bulk_g2s(stage + off_ks(pool), src.ks + (size_t)blk0 * 256, (uint32_t)(nblk * 256), bar);
+  bulk_g2s(stage + off_kz(pool), src.kz + (size_t)blk0 * 128, (uint32_t)(nblk * 128), bar);
   if (pool == 0) {   // two 64-channel boxes of kTF rows, 128-byte swizzle
     const int row = win - p.g.k_off_fp;
     tensor_g2s_4d(stage + kOffV, &p.fp_map, 0, row, h, b, bar);
@@ -496,9 +496,9 @@ __device__ __forceinline__ void consume_pool(WarpState& st, const DecodeParams& 
   const int t0 = 2 * t + (t & 1), t1 = 2 * t + 1 - (t & 1);
   const int blk = slice >> p.kblock_shift;   // windows start on multiples of the largest key block
   LaneOffsets o;
-  o.k = kOffK + (slice + pg) * 64 + 16 * t;
-  o.ks = kOffKS + blk * 256 + 64 * t;
-  o.kz = kOffKZ + blk * 128 + 32 * t;
+  o.k = off_k(POOL) + (slice + pg) * 64 + 16 * t;
+  o.ks = off_ks(POOL) + blk * 256 + 64 * t;
+  o.kz = off_kz(POOL) + blk * 128 + 32 * t;
   int step = 0;
   if (POOL == 0) {
     o.va = kOffV + fp_box_offset(slice + t0, 2 * g);   // swizzled half boxes

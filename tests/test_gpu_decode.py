@@ -74,7 +74,7 @@ def test_int4_only_4096_tokens_with_full_residual_window():
 @pytest.mark.parametrize("grid_cap", GRID_CAPS)
 def test_mixed_pools_fused_append_every_step(hq, hkv, grid_cap, monkeypatch):
     """Mixed bf16/INT4/INT2 pages (25/50/25), one fused append per decode step across a flush; with a grid limit
-    a CTA streams up to 30 tiles of three pools through the three-stage ring and carries its softmax state across."""
+    a CTA streams up to 30 tiles of three pools through the shared-memory ring and carries its softmax state across."""
     apply_grid_cap(monkeypatch, grid_cap, hkv)
     classes = seeded_classes(96, 3)
     ocache, gcache, new_k, new_v, queries = both_caches(22 + hq, hq=hq, hkv=hkv, tokens=96 * 64, page=64, classes=classes,
