@@ -40,6 +40,9 @@ template <bool BF16>
 __global__ void __launch_bounds__(64) pack_k_int4_kernel(PackArgs a, uint8_t* packed, __half* scale, uint8_t* zero,
                                                          int64_t packed_bstride, int64_t scale_bstride, int64_t zero_bstride,
                                                          int k_block, int64_t first_block) {
+  // A flush launches the value pack behind this kernel with programmatic stream serialization: the two read
+  // different halves of the residual window and write different arenas, so they may run side by side.
+  launch_dependents();
   const int64_t blk = first_block + blockIdx.x;
   const int head = blockIdx.y, req = blockIdx.z, c = threadIdx.x;
   const int64_t blocks_per_head = a.capacity / k_block;
@@ -141,40 +144,45 @@ template <bool BF16>
 __global__ void __launch_bounds__(128) pack_v_int2_kernel(PackArgs a, uint8_t* packed, __half* scale, uint8_t* zero,
                                                           int64_t packed_bstride, int64_t scale_bstride, int64_t zero_bstride,
                                                           int group) {
+  launch_dependents();   // in a flush the ring kernel follows; it waits for this grid before it touches the ring
   const int64_t i = (int64_t)blockIdx.x * 4 + (threadIdx.x >> 5);
-  if (i >= a.count) return;
-  const int head = blockIdx.y, req = blockIdx.z, lane = threadIdx.x & 31;
-  const int64_t s = a.index ? a.index[i] : i;
-  const uint16_t* src = reinterpret_cast<const uint16_t*>(reinterpret_cast<const uint8_t*>(a.src) + req * a.src_bstride) +
-                        ((int64_t)head * a.src_rows + s) * 128;
-  const uint2 w = *reinterpret_cast<const uint2*>(src + 4 * lane);
-  float x[4] = {raw_to_float<BF16>((uint16_t)(w.x & 0xffffu)), raw_to_float<BF16>((uint16_t)(w.x >> 16)),
-                raw_to_float<BF16>((uint16_t)(w.y & 0xffffu)), raw_to_float<BF16>((uint16_t)(w.y >> 16))};
-  float lo = fminf(fminf(x[0], x[1]), fminf(x[2], x[3]));
-  float hi = fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3]));
-  const int lanes = group / 4;  // lanes per group: 8, 16 or 32
-  for (int d = 1; d < lanes; d <<= 1) {
-    lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, d));
-    hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, d));
+  if (i < a.count) {
+    const int head = blockIdx.y, req = blockIdx.z, lane = threadIdx.x & 31;
+    const int64_t s = a.index ? a.index[i] : i;
+    const uint16_t* src = reinterpret_cast<const uint16_t*>(reinterpret_cast<const uint8_t*>(a.src) + req * a.src_bstride) +
+                          ((int64_t)head * a.src_rows + s) * 128;
+    const uint2 w = *reinterpret_cast<const uint2*>(src + 4 * lane);
+    float x[4] = {raw_to_float<BF16>((uint16_t)(w.x & 0xffffu)), raw_to_float<BF16>((uint16_t)(w.x >> 16)),
+                  raw_to_float<BF16>((uint16_t)(w.y & 0xffffu)), raw_to_float<BF16>((uint16_t)(w.y >> 16))};
+    float lo = fminf(fminf(x[0], x[1]), fminf(x[2], x[3]));
+    float hi = fmaxf(fmaxf(x[0], x[1]), fmaxf(x[2], x[3]));
+    const int lanes = group / 4;  // lanes per group: 8, 16 or 32
+    for (int d = 1; d < lanes; d <<= 1) {
+      lo = fminf(lo, __shfl_xor_sync(0xffffffffu, lo, d));
+      hi = fmaxf(hi, __shfl_xor_sync(0xffffffffu, hi, d));
+    }
+    lo = fminf(lo, 0.f);
+    hi = fmaxf(hi, 0.f);
+    const float sc = fmaxf(__fdiv_rn(__fsub_rn(hi, lo), 3.f), 1.0e-6f);
+    const float zp = fminf(fmaxf(rintf(__fdiv_rn(-lo, sc)), 0.f), 3.f);
+    uint32_t out = 0;
+  #pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const uint32_t q = (uint32_t)fminf(fmaxf(rintf(__fadd_rn(__fdiv_rn(x[e], sc), zp)), 0.f), 3.f);
+      out |= q << (2 * e);
+    }
+    const int64_t row = (int64_t)head * a.capacity + a.dst_start + i;
+    packed[req * packed_bstride + row * 32 + lane] = (uint8_t)out;
+    if ((lane & (lanes - 1)) == 0) {
+      const int groups = 128 / group;
+      const int64_t m = row * groups + lane / lanes;
+      reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(scale) + req * scale_bstride)[m] = __float2half_rn(sc);
+      zero[req * zero_bstride + m] = (uint8_t)zp;
+    }
   }
-  lo = fminf(lo, 0.f);
-  hi = fmaxf(hi, 0.f);
-  const float sc = fmaxf(__fdiv_rn(__fsub_rn(hi, lo), 3.f), 1.0e-6f);
-  const float zp = fminf(fmaxf(rintf(__fdiv_rn(-lo, sc)), 0.f), 3.f);
-  uint32_t out = 0;
-#pragma unroll
-  for (int e = 0; e < 4; ++e) {
-    const uint32_t q = (uint32_t)fminf(fmaxf(rintf(__fadd_rn(__fdiv_rn(x[e], sc), zp)), 0.f), 3.f);
-    out |= q << (2 * e);
-  }
-  const int64_t row = (int64_t)head * a.capacity + a.dst_start + i;
-  packed[req * packed_bstride + row * 32 + lane] = (uint8_t)out;
-  if ((lane & (lanes - 1)) == 0) {
-    const int groups = 128 / group;
-    const int64_t m = row * groups + lane / lanes;
-    reinterpret_cast<__half*>(reinterpret_cast<uint8_t*>(scale) + req * scale_bstride)[m] = __float2half_rn(sc);
-    zero[req * zero_bstride + m] = (uint8_t)zp;
-  }
+  // In a flush this grid runs beside the key pack in front of it.  The ring kernel behind it waits for this
+  // grid only, so this grid must not complete before the key pack has: every thread passes here on its way out.
+  grid_dependency_wait();
 }
 
 // ---- row gather (bf16-value pool) ------------------------------------------
@@ -245,6 +253,7 @@ __global__ void flush_ring_kernel(RingArgs r, int ring_tokens, int flush_tokens,
     int64_t* dl = reinterpret_cast<int64_t*>(reinterpret_cast<uint8_t*>(i2_logical) + b * meta_bstride) + meta_dst;
     for (int i = threadIdx.x; i < flush_tokens; i += blockDim.x) { dg[i] = gl[i]; dl[i] = lg[i]; }
   }
+  grid_dependency_wait();   // the pack kernels read the rows that are moved and the length that is reset below
   __syncthreads();
   for (int col = threadIdx.x; col < r.num_heads * 16; col += blockDim.x) {
     const int h = col >> 4, piece = col & 15;

@@ -238,13 +238,30 @@ int launch_pack_k(const PackArgs& a, int batch, uint8_t* packed, void* scale, ui
   ++g_launches;
   return cudaGetLastError() == cudaSuccess ? R2K_OK : R2K_ERR_CUDA;
 }
+// A launch that may start while the kernel in front of it on the stream is still running, once that kernel has
+// let its dependents go (programmatic stream serialization); `overlap` false gives an ordinary launch.
+template <typename... Params, typename... Args>
+cudaError_t launch_behind(void (*kernel)(Params...), dim3 grid, dim3 block, cudaStream_t st, bool overlap, Args... args) {
+  cudaLaunchAttribute attr[1];
+  attr[0].id = cudaLaunchAttributeProgrammaticStreamSerialization;
+  attr[0].val.programmaticStreamSerializationAllowed = overlap ? 1 : 0;
+  cudaLaunchConfig_t cfg = {};
+  cfg.gridDim = grid;
+  cfg.blockDim = block;
+  cfg.stream = st;
+  cfg.attrs = attr;
+  cfg.numAttrs = 1;
+  return cudaLaunchKernelEx(&cfg, kernel, static_cast<Params>(args)...);
+}
+
 template <bool BF16>
 int launch_pack_v2(const PackArgs& a, int batch, uint8_t* packed, void* scale, uint8_t* zero, int64_t pb, int64_t sb, int64_t zb,
-                   int group, cudaStream_t st) {
+                   int group, cudaStream_t st, bool overlap = false) {
   dim3 grid((unsigned)((a.count + 3) / 4), (unsigned)a.num_heads, (unsigned)batch);
-  pack_v_int2_kernel<BF16><<<grid, 128, 0, st>>>(a, packed, reinterpret_cast<__half*>(scale), zero, pb, sb, zb, group);
+  const cudaError_t err = launch_behind(pack_v_int2_kernel<BF16>, grid, dim3(128), st, overlap, a, packed,
+                                        reinterpret_cast<__half*>(scale), zero, pb, sb, zb, group);
   ++g_launches;
-  return cudaGetLastError() == cudaSuccess ? R2K_OK : R2K_ERR_CUDA;
+  return err == cudaSuccess ? R2K_OK : R2K_ERR_CUDA;
 }
 
 RingArgs ring_args(const R2KGeom* g, const R2KCacheView* v) {
@@ -752,6 +769,9 @@ int r2k_flush_recent(const R2KGeom* geom, const R2KCacheView* view, int32_t ring
     return R2K_ERR_NULL;
   if ((i2_global == nullptr) != (i2_logical == nullptr)) return R2K_ERR_NULL;
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  DeviceInfo* dev;
+  rc = device_info(&dev);
+  if (rc) return rc;
   const bool bf16 = geom->dtype == R2K_DTYPE_BF16;
   PackArgs ka{reinterpret_cast<const uint16_t*>(view->recent_k), view->recent_k_bstride, geom->recent_capacity, nullptr,
               flush_tokens, geom->k_capacity, k_dst, geom->num_kv_heads};
@@ -768,15 +788,20 @@ int r2k_flush_recent(const R2KGeom* geom, const R2KCacheView* view, int32_t ring
   uint8_t* vp = const_cast<uint8_t*>(view->i2_packed);
   void* vs = const_cast<void*>(view->i2_scale);
   uint8_t* vz = const_cast<uint8_t*>(view->i2_zero);
+  // The three launches overlap where they may: the value pack runs beside the key pack (different halves of the
+  // ring, different arenas) and only completes after it; the ring kernel copies the flushed tokens' indices, then
+  // waits for both packs before it moves rows and resets the length.  The ring kernel does not let ITS dependents go
+  // early: a decode launch behind a flush must find the pools complete.
   rc = bf16 ? launch_pack_v2<true>(va, geom->batch, vp, vs, vz, view->i2_packed_bstride, view->i2_scale_bstride,
-                                   view->i2_zero_bstride, geom->v2_group, st)
+                                   view->i2_zero_bstride, geom->v2_group, st, dev->pdl)
             : launch_pack_v2<false>(va, geom->batch, vp, vs, vz, view->i2_packed_bstride, view->i2_scale_bstride,
-                                    view->i2_zero_bstride, geom->v2_group, st);
+                                    view->i2_zero_bstride, geom->v2_group, st, dev->pdl);
   if (rc) return rc;
-  flush_ring_kernel<<<geom->batch, 256, 0, st>>>(ring_args(geom, view), ring_tokens, flush_tokens, i2_global, i2_logical,
-                                                 meta_bstride, v_meta_dst);
+  const cudaError_t err = launch_behind(flush_ring_kernel, dim3((unsigned)geom->batch), dim3(256), st, dev->pdl,
+                                        ring_args(geom, view), (int)ring_tokens, (int)flush_tokens, i2_global, i2_logical,
+                                        meta_bstride, v_meta_dst);
   ++g_launches;
-  return cudaGetLastError() == cudaSuccess ? R2K_OK : R2K_ERR_CUDA;
+  return err == cudaSuccess ? R2K_OK : R2K_ERR_CUDA;
 }
 
 }  // extern "C"
