@@ -103,6 +103,41 @@ def test_mixed_pools_fused_append_every_step(hq, hkv, grid_cap, monkeypatch):
     assert ex.device_status() == 0
 
 
+@pytest.mark.parametrize("hq,hkv", [(3, 3), (4, 2), (3, 1), (8, 2), (5, 1), (12, 2), (7, 1), (8, 1)])
+def test_every_group_width(hq, hkv):
+    """Query heads per kv head from 1 (no grouping) to 8, a single kv head included: the MMA's eight head columns
+    are padded for narrower groups and the padding must reach neither the output nor the appended rows.  Mixed pages,
+    fused appends, the Hadamard epilogue and the state output."""
+    classes = seeded_classes(24, 60 + hq)
+    s = 24 * 64
+    ocache, gcache, new_k, new_v, queries = both_caches(70 + 8 * hq + hkv, hq=hq, hkv=hkv, tokens=s, page=64, classes=classes,
+                                                        appends=6, n_queries=8, append_capacity=256)
+    ex = make_executor(gcache, hq)
+    exh = make_executor(gcache, hq, output_hadamard=True)
+    k, v = new_k.cuda(), new_v.cuda()
+    for i in range(6):
+        q = queries[i]
+        out = ex.decode_f32(q.cuda(), append=(k[i].unsqueeze(0).contiguous(), v[i].unsqueeze(0).contiguous(), s + i, s + i))
+        gcache.recent_fp_pool.active_length += 1
+        O.append_token(ocache, new_k[i], new_v[i], s + i, s + i)
+        assert_close(out, O.decode_fp32(q.float(), ocache), f"group of {hq // hkv}, step {i}")
+    arena_equal(ocache, gcache)
+    q = queries[6]
+    got = ex(q.cuda())
+    assert got.shape == (1, hq, 128) and got.dtype == torch.bfloat16
+    assert_close(got, O.decode(q, ocache), "element-type output")
+    # the epilogue rotates the rounded output: checked against the oracle's transform of this very output, so that
+    # the attention tolerance (which a rounding before a 128-term sum amplifies) stays out of it; one ulp of slack
+    rotated = O.fwht128(got.float().cpu()).to(torch.bfloat16).float()
+    assert ((exh(q.cuda()).float().cpu() - rotated).abs() <= 2.0 ** -7 * rotated.abs() + 1e-6).all()
+    top, den, acc = O.decode_state(queries[7].float(), ocache)
+    st = ex.decode_state(queries[7].cuda()).cpu()
+    assert st.shape == (1, hq, 130)
+    assert torch.allclose(st[..., 0] + torch.log(st[..., 1]), top + torch.log(den), atol=2e-3)
+    assert_close(st[..., 2:] / st[..., 1:2], acc / den.unsqueeze(-1), "state output")
+    assert ex.device_status() == 0
+
+
 @pytest.mark.parametrize("grid_cap", (None, "heads", "3"))
 def test_stacked_batch_matches_per_request_oracle(grid_cap, monkeypatch):
     """Homogeneous batch (B=3): stacked arenas, per-request oracle; fused append and a batched flush."""
