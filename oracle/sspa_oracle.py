@@ -405,14 +405,19 @@ def merge_state(a, b):
     return top, a[1] * wa + b[1] * wb, a[2] * wa.unsqueeze(-1) + b[2] * wb.unsqueeze(-1)
 
 
-def pool_tensors(cache: OracleCache):
+def pool_tensors(cache: OracleCache, round_int4_values: bool = True):
     """Dequantised fp32 (K, V) of the four pools in the reference's merge order
-    (bf16-V, INT4-V, INT2-V, residual); triton_fourq_attention.py:17-38, 91-121."""
+    (bf16-V, INT4-V, INT2-V, residual); triton_fourq_attention.py:17-38, 91-121.
+
+    The reference's CPU decoder takes the INT4 values through ``PackedTensor.dequantize``, which rounds
+    ``code * scale`` to the cache's element type (packed_kv_layout.py:30-32); its GPU kernel multiplies in fp32
+    and does not round (triton_fourq_splitk.py:789-795).  ``round_int4_values=False`` gives the second form, which
+    a test uses to tell a kernel's own error from that rounding."""
     n_i2 = cache.i2_active
     spans = ((cache.k_offsets[0], cache.n_fp), (cache.k_offsets[1], cache.n_i4), (cache.k_offsets[2], n_i2))
     values = (
         cache.fp_v.float(),
-        dequantize_v_int4(cache.i4_packed, cache.i4_scale, round_to=cache.dtype),
+        dequantize_v_int4(cache.i4_packed, cache.i4_scale, round_to=cache.dtype if round_int4_values else None),
         dequantize_v_int2(cache.i2_packed[:, :n_i2], cache.i2_scale[:, :n_i2], cache.i2_zero[:, :n_i2], cache.v2_group),
     )
     out = []
@@ -424,7 +429,7 @@ def pool_tensors(cache: OracleCache):
     return out
 
 
-def decode_state(query, cache: OracleCache, sm_scale=None, chunk=None):
+def decode_state(query, cache: OracleCache, sm_scale=None, chunk=None, round_int4_values: bool = True):
     """Un-normalised merged (max, sum-exp, weighted-V) over every pool.
 
     ``chunk`` bounds memory for very long caches by applying the same
@@ -434,7 +439,7 @@ def decode_state(query, cache: OracleCache, sm_scale=None, chunk=None):
         query = query[:, :, 0]
     scale = float(sm_scale) if sm_scale is not None else query.shape[-1] ** -0.5
     state = None
-    for k, v in pool_tensors(cache):
+    for k, v in pool_tensors(cache, round_int4_values):
         step = k.shape[1] if chunk is None else int(chunk)
         for s0 in range(0, k.shape[1], step):
             part = partial_state(query, k[:, s0 : s0 + step], v[:, s0 : s0 + step], scale)
@@ -455,9 +460,9 @@ def decode(query, cache: OracleCache, sm_scale=None, output_hadamard=False, chun
     return out
 
 
-def decode_fp32(query, cache: OracleCache, sm_scale=None):
+def decode_fp32(query, cache: OracleCache, sm_scale=None, round_int4_values: bool = True):
     """Same as :func:`decode` without the final rounding to the query dtype."""
-    top, den, acc = decode_state(query, cache, sm_scale)
+    top, den, acc = decode_state(query, cache, sm_scale, round_int4_values=round_int4_values)
     return acc / den.unsqueeze(-1)
 
 

@@ -191,6 +191,48 @@ def test_fp16_cache_and_wide_blocks():
     assert ex(queries[1].cuda()).dtype == torch.bfloat16
 
 
+@pytest.mark.parametrize("dtype", [torch.bfloat16, torch.float16])
+@pytest.mark.parametrize("k_block,v2_group", [(32, 32), (32, 64), (64, 32), (64, 64), (128, 32), (128, 128), (32, 128)])
+def test_block_and_group_sizes_through_a_flush(k_block, v2_group, dtype):
+    """Key calibration blocks of 32 / 64 / 128 tokens and INT2 groups of 32 / 64 / 128 channels, both element types:
+    a history that does not end on a key block (the flush re-quantises the tail block), 130 appends through one
+    flush, arenas bit for bit, decode within tolerance before and after."""
+    classes = torch.tensor([2, 1, 5, 2, 5, 1, 2])
+    s = 7 * 32
+    ocache, gcache, new_k, new_v, queries = both_caches(90 + k_block + v2_group, hq=16, hkv=2, tokens=s, page=32, classes=classes,
+                                                        appends=130, n_queries=3, dtype=dtype, k_block=k_block,
+                                                        v2_group=v2_group, append_capacity=256)
+    ex = make_executor(gcache, 16)
+    stats = R.DynamicCacheStats()
+    k, v = new_k.cuda(), new_v.cuda()
+
+    def check(qi, what):
+        # 350 tokens of seeded noise make peaked attention: single INT4-value tokens carry most of a head's weight.
+        # The reference's CPU decoder rounds code * scale of INT4 values to the element type, its GPU kernel and
+        # this one do not; with weights like these that rounding alone moves the CPU result by more than the
+        # tolerance.  So: within tolerance of the unrounded form, and of the rounded form once its own shift is allowed.
+        q = queries[qi]
+        got = ex.decode_f32(q.cuda())
+        plain = O.decode_fp32(q.float(), ocache, round_int4_values=False)
+        assert_close(got, plain, what)
+        rounded = O.decode_fp32(q.float(), ocache)
+        slack = (rounded - plain).abs()
+        assert ((got.cpu() - rounded).abs() <= 2e-3 + 1e-2 * rounded.abs() + slack).all(), what
+
+    check(0, "before the appends")
+    flushed = 0
+    for i in range(130):
+        O.append_token(ocache, new_k[i], new_v[i], s + i, s + i)
+        flushed += bool(R.append_generated_token(gcache, k[i].unsqueeze(1), v[i].unsqueeze(1), global_token_index=s + i,
+                                                 logical_position=s + i, stats=stats))
+        if i == 126:
+            check(1, "full window")
+    assert flushed == 1
+    arena_equal(ocache, gcache)
+    check(2, "after the flush")
+    assert ex.device_status() == 0
+
+
 def test_only_residual_window_and_only_history():
     classes = torch.tensor([0, 0])       # every page evicted: attention over the residual window alone
     ocache, gcache, new_k, new_v, queries = both_caches(33, hq=16, hkv=2, tokens=64, page=32, classes=classes, appends=5)
