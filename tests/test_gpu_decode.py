@@ -233,6 +233,28 @@ def test_block_and_group_sizes_through_a_flush(k_block, v2_group, dtype):
     assert ex.device_status() == 0
 
 
+@pytest.mark.parametrize("p_fp,p_i4", [(0.25, 0.5), (0.0, 1.0), (0.0, 0.0), (1.0, 0.0)])
+def test_peaked_attention(p_fp, p_i4):
+    """Queries three times as long as usual: a few tokens take most of every head's weight, so nothing averages
+    out and every rounding of a probability or a value shows.  Mixed pages and each value format alone, six seeds."""
+    for seed in range(6):
+        classes = seeded_classes(32, 200 + seed, p_fp=p_fp, p_i4=p_i4)
+        ocache, gcache, new_k, new_v, queries = both_caches(300 + seed, hq=16, hkv=2, tokens=32 * 64, page=64, classes=classes,
+                                                            appends=3, n_queries=1)
+        for i in range(3):
+            O.append_token(ocache, new_k[i], new_v[i], 2048 + i, 2048 + i)
+            R.append_generated_token(gcache, new_k[i].cuda().unsqueeze(1), new_v[i].cuda().unsqueeze(1),
+                                     global_token_index=2048 + i, logical_position=2048 + i, stats=R.DynamicCacheStats())
+        q = (queries[0].float() * 3.0).to(torch.bfloat16)
+        got = make_executor(gcache, 16).decode_f32(q.cuda())
+        plain = O.decode_fp32(q.float(), ocache, round_int4_values=False)
+        assert_close(got, plain, f"seed {seed}")
+        # the CPU decoder's rounding of INT4 values moves its own result by `slack` (see the test above)
+        rounded = O.decode_fp32(q.float(), ocache)
+        slack = (rounded - plain).abs()
+        assert ((got.cpu() - rounded).abs() <= 2e-3 + 1e-2 * rounded.abs() + slack).all(), f"seed {seed}, rounded form"
+
+
 def test_only_residual_window_and_only_history():
     classes = torch.tensor([0, 0])       # every page evicted: attention over the residual window alone
     ocache, gcache, new_k, new_v, queries = both_caches(33, hq=16, hkv=2, tokens=64, page=32, classes=classes, appends=5)
