@@ -255,6 +255,26 @@ def test_peaked_attention(p_fp, p_i4):
         assert ((got.cpu() - rounded).abs() <= 2e-3 + 1e-2 * rounded.abs() + slack).all(), f"seed {seed}, rounded form"
 
 
+def test_explicit_softmax_scale_and_four_dimensional_query():
+    """A softmax scale other than 128 ** -0.5 (the executor's constructor takes one), and the query given as
+    [B, Hq, 1, 128], the form the attention manager hands over."""
+    classes = seeded_classes(16, 77)
+    ocache, gcache, new_k, new_v, queries = both_caches(78, hq=16, hkv=2, tokens=16 * 64, page=64, classes=classes, appends=2)
+    for i in range(2):
+        O.append_token(ocache, new_k[i], new_v[i], 1024 + i, 1024 + i)
+        R.append_generated_token(gcache, new_k[i].cuda().unsqueeze(1), new_v[i].cuda().unsqueeze(1),
+                                 global_token_index=1024 + i, logical_position=1024 + i, stats=R.DynamicCacheStats())
+    ws = R.allocate_splitk_workspace(gcache, num_query_heads=16)
+    q = queries[0]
+    for scale in (0.03, 0.2):
+        ex = R.SplitKExecutor(gcache.arenas, ws, cache=gcache, sm_scale=scale)
+        assert_close(ex.decode_f32(q.cuda()), O.decode_fp32(q.float(), ocache, sm_scale=scale), f"scale {scale}")
+    ex = make_executor(gcache, 16)
+    flat = ex(q.cuda()).clone()
+    assert torch.equal(ex(q.cuda().unsqueeze(2)), flat)
+    assert_close(flat, O.decode(q, ocache), "default scale")
+
+
 def test_only_residual_window_and_only_history():
     classes = torch.tensor([0, 0])       # every page evicted: attention over the residual window alone
     ocache, gcache, new_k, new_v, queries = both_caches(33, hq=16, hkv=2, tokens=64, page=32, classes=classes, appends=5)
