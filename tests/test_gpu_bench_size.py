@@ -115,3 +115,30 @@ def test_single_request_128k_shard_two_level_merge():
     assert torch.allclose(state[..., 0] + state[..., 1].log(), top + den.log(), atol=2e-3)
     assert_close(state[..., 2:] / state[..., 1:2], acc / den.unsqueeze(-1), "un-normalised state")
     assert ex.device_status() == 0
+
+
+@pytest.mark.parametrize("tokens,batch", [(32768, 4), (131072, 1)])
+def test_repeated_launches_give_the_same_bits(tokens, batch):
+    """Which CTA of a head arrives last at the merge differs from launch to launch; the result must not: partials
+    are folded in slot order whoever folds them.  Sixty launches of the same step (nine partials per head merged in
+    one level; 74 per head merged in two), every output bit for bit the first one."""
+    hq, hkv = 16, 2
+    classes = page_classes(tokens // PAGE, 31, 0.25 if batch > 1 else 0.0, 0.5)
+    singles = []
+    for b in range(batch):
+        key, value = synth_kv(tokens, 4000 + b, "cuda", hkv=hkv)
+        singles.append(make_executor(R.build_three_precision_cache(
+            key, value, make_plan(classes, PAGE, RING), page_size=PAGE, key_quantization_superblock=K_BLOCK,
+            int2_group_size=V2_GROUP, compact_key_append_capacity=RING, recent_flush_size=RING), hq))
+        del key, value
+    ex = singles[0] if batch == 1 else R.stack_homogeneous_splitk_executors(singles)
+    g = torch.Generator().manual_seed(3)
+    q = torch.randn(batch, hq, 128, generator=g).to(torch.bfloat16).cuda()
+    first = ex.decode_f32(q).clone()
+    state = ex.decode_state(q).clone()
+    assert torch.isfinite(first).all()
+    for i in range(60):
+        assert torch.equal(ex.decode_f32(q), first), f"launch {i}"
+    for i in range(10):
+        assert torch.equal(ex.decode_state(q), state), f"state, launch {i}"
+    assert ex.device_status() == 0
