@@ -856,7 +856,7 @@ THINKER = dict(layers=36, hidden=2048, hq=16, hkv=2, mlp=11008, vocab=151936, th
 
 class SyntheticThinker:
     """A Qwen2.5-Omni-3B-shaped text decoder with random weights (~N(0, 0.02), bf16): RMSNorm, q/k/v projections
-    with bias, multimodal RoPE (text positions: the three axes agree), packed-KV attention through
+    with bias (one GEMM), multimodal RoPE (text positions: the three axes agree), packed-KV attention through
     PackedKVAttentionManager (kernel_backend "cuda_sm100"), output projection, SwiGLU MLP; final norm, LM head,
     argmax.  Every layer's cache holds `tokens` prefilled tokens per request, packed from random bf16
     activations with seeded page precisions.  One decode step is captured into a CUDA graph: token ids,
@@ -885,13 +885,14 @@ class SyntheticThinker:
         self.layers = []
         t_build = time.perf_counter()
         for l in range(c["layers"]):
+            # query, key and value projections as one GEMM: the manager hands its output to the one-launch prologue
             attn = types.SimpleNamespace(
-                head_dim=128, q_proj=linear(c["hidden"], c["hq"] * 128, True), k_proj=linear(c["hidden"], c["hkv"] * 128, True),
-                v_proj=linear(c["hidden"], c["hkv"] * 128, True), o_proj=linear(c["hq"] * 128, c["hidden"], False))
+                head_dim=128, qkv_proj=linear(c["hidden"], (c["hq"] + 2 * c["hkv"]) * 128, True),
+                o_proj=linear(c["hq"] * 128, c["hidden"], False))
             self.layers.append(types.SimpleNamespace(
                 attn=attn, ln1=torch.ones(c["hidden"], device=device, dtype=torch.bfloat16),
                 ln2=torch.ones(c["hidden"], device=device, dtype=torch.bfloat16),
-                gate=linear(c["hidden"], c["mlp"], False), up=linear(c["hidden"], c["mlp"], False),
+                gate_up=linear(c["hidden"], 2 * c["mlp"], False),    # gate and up projections as one GEMM
                 down=linear(c["mlp"], c["hidden"], False)))
             classes = page_classes(c["tokens"] // c["page"], 300 + l, c["mix"][0], c["mix"][1])
             caches = []
@@ -925,7 +926,8 @@ class SyntheticThinker:
             h = F.rms_norm(x, (c["hidden"],), layer.ln1, 1e-6)
             x = x + self.manager.active_forward(l, layer.attn, h, (cos, sin), append_indices=self.idx)
             h = F.rms_norm(x, (c["hidden"],), layer.ln2, 1e-6)
-            x = x + layer.down(F.silu(layer.gate(h)) * layer.up(h))
+            gate, up = layer.gate_up(h).chunk(2, dim=-1)
+            x = x + layer.down(F.silu(gate) * up)
         h = F.rms_norm(x, (c["hidden"],), self.final_norm, 1e-6)
         logits = h.view(B, c["hidden"]) @ self.lm_head.t()
         self.tok.copy_(logits.argmax(dim=-1))

@@ -332,6 +332,20 @@ int r2k_qk_mrope(const void* q, const void* k, void* q_out, void* k_out, int32_t
                  int32_t rot_dtype, const int64_t cos_strides[4], const int64_t sin_strides[4], int32_t section0,
                  int32_t section1, int32_t apply_hadamard, void* stream);
 
+/* The whole prologue of a decode step in one launch: query rows [B,Hq,128] and new key rows [B,Hkv,128] rotated as
+ * by r2k_qk_mrope (one token per request; Hadamard when key_hadamard), new value rows [B,Hkv,128] brought along
+ * (copied, or Hadamard-transformed as by r2k_fwht128 when value_hadamard).  The three inputs may be slices of one
+ * fused projection output: `*_bstride` is the number of elements between two requests' rows (a request's heads are
+ * contiguous; a multiple of 4); the outputs are contiguous and are what r2k_decode takes as q and as the rows to
+ * append.  The launch lets the decode launch behind it start early, like r2k_qk_mrope.  Same arithmetic, bit for
+ * bit, as the two calls it replaces.  Covers what _project_qkv does after the projections
+ * (r2omni/sspa/integration/qwen_sspa_attention.py:1216-1249, and the value rotation of :1780). */
+int r2k_qkv_prologue(const void* q, int64_t q_bstride, const void* k, int64_t k_bstride, const void* v, int64_t v_bstride,
+                     void* q_out, void* k_out, void* v_out, int32_t dtype, int32_t batch, int32_t num_q_heads,
+                     int32_t num_kv_heads, const void* cos, const void* sin, int32_t rot_dtype,
+                     const int64_t cos_strides[4], const int64_t sin_strides[4], int32_t section0, int32_t section1,
+                     int32_t key_hadamard, int32_t value_hadamard, void* stream);
+
 /* ---- residual window ---------------------------------------------------- */
 
 /*

@@ -13,7 +13,7 @@ FLAG_OUTPUT_HADAMARD, FLAG_OUT_F32, FLAG_OUT_STATE = 1, 2, 4
 EXPORTS = (
     "r2k_status_string", "r2k_launch_count", "r2k_decode_workspace_bytes", "r2k_decode_workspace_init", "r2k_decode",
     "r2k_decode_static", "r2k_decode_static_status", "r2k_decode_static_reset", "r2k_decode_device_status", "r2k_merge_states", "r2k_pack_k_int4", "r2k_pack_v_int4", "r2k_pack_v_int2",
-    "r2k_gather_rows", "r2k_fwht128", "r2k_qk_mrope", "r2k_append_recent", "r2k_flush_recent",
+    "r2k_gather_rows", "r2k_fwht128", "r2k_qk_mrope", "r2k_qkv_prologue", "r2k_append_recent", "r2k_flush_recent",
     "r2k_exchange_bytes", "r2k_exchange_create", "r2k_exchange_open", "r2k_exchange_close", "r2k_decode_exchange",
     "r2k_decode_host_staging_bytes", "r2k_decode_host",
 )

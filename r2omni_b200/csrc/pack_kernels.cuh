@@ -330,6 +330,12 @@ struct MropeArgs {
   const void* cos; const void* sin;
   int64_t cos_stride[4], sin_stride[4];   // elements: axis, request, token, channel
   int batch, hq, hkv, tokens, section0, section1, rot_dtype, hadamard;   // rot_dtype: R2K_DTYPE_* or 2 for float32
+  // The whole prologue of a decode step (v != nullptr): the value rows pass through the same launch (copied, or
+  // Hadamard-transformed when v_hadamard), and the three inputs may be slices of one fused projection: elements
+  // between two requests' rows (a request's heads and tokens stay contiguous); the outputs are contiguous.
+  const uint16_t* v; uint16_t* v_out;
+  int64_t q_bstride, k_bstride, v_bstride;
+  int v_hadamard;
 };
 
 __device__ __forceinline__ float load_rot(const void* base, int64_t index, int dtype) {
@@ -346,15 +352,23 @@ __global__ void mrope_rows_kernel(MropeArgs a) {
   launch_dependents();
   const int64_t row = (int64_t)blockIdx.x * (blockDim.x >> 5) + (threadIdx.x >> 5);
   const int lane = threadIdx.x & 31;
-  const int heads = a.hq + a.hkv;
+  const int heads = a.hq + a.hkv + (a.v != nullptr ? a.hkv : 0);
   if (row >= (int64_t)a.batch * heads * a.tokens) return;
   const int request = (int)(row / ((int64_t)heads * a.tokens));
   const int local = (int)(row - (int64_t)request * heads * a.tokens);
   const int head = local / a.tokens, token = local - head * a.tokens;
-  const bool is_q = head < a.hq;
-  const int64_t off = is_q ? (((int64_t)request * a.hq + head) * a.tokens + token) * 128
-                           : (((int64_t)request * a.hkv + (head - a.hq)) * a.tokens + token) * 128;
-  const uint2 raw = *reinterpret_cast<const uint2*>((is_q ? a.q : a.k) + off + 4 * lane);
+  const int which = head < a.hq ? 0 : (head < a.hq + a.hkv ? 1 : 2);   // query, key or value row
+  const int h = which == 0 ? head : (which == 1 ? head - a.hq : head - a.hq - a.hkv);
+  const int nh = which == 0 ? a.hq : a.hkv;
+  const int64_t in_row = ((int64_t)h * a.tokens + token) * 128;
+  const int64_t off = (((int64_t)request * nh + h) * a.tokens + token) * 128;   // in the contiguous output
+  const uint16_t* src = which == 0 ? a.q + request * a.q_bstride : (which == 1 ? a.k + request * a.k_bstride : a.v + request * a.v_bstride);
+  uint16_t* dst = which == 0 ? a.q_out : (which == 1 ? a.k_out : a.v_out);
+  const uint2 raw = *reinterpret_cast<const uint2*>(src + in_row + 4 * lane);
+  if (which == 2 && !a.v_hadamard) {   // a value row that is only brought into place
+    *reinterpret_cast<uint2*>(dst + off + 4 * lane) = raw;
+    return;
+  }
   float x[4];
   if (BF16) {
     x[0] = __uint_as_float(raw.x << 16); x[1] = __uint_as_float(raw.x & 0xffff0000u);
@@ -365,19 +379,24 @@ __global__ void mrope_rows_kernel(MropeArgs a) {
     x[0] = lo.x; x[1] = lo.y; x[2] = hi.x; x[3] = hi.y;
   }
   float r[4];
+  if (which == 2) {
 #pragma unroll
-  for (int e = 0; e < 4; ++e) {
-    const int d = 4 * lane + e, sd = d & 63;
-    const float other = __shfl_xor_sync(0xffffffffu, x[e], 16);   // channel d +- 64 lives 16 lanes away
-    const float rotated = lane < 16 ? -other : other;
-    const int axis = sd < a.section0 ? 0 : (sd < a.section0 + a.section1 ? 1 : 2);
-    const float c = load_rot(a.cos, axis * a.cos_stride[0] + request * a.cos_stride[1] + token * a.cos_stride[2] + d * a.cos_stride[3],
-                             a.rot_dtype);
-    const float s = load_rot(a.sin, axis * a.sin_stride[0] + request * a.sin_stride[1] + token * a.sin_stride[2] + d * a.sin_stride[3],
-                             a.rot_dtype);
-    r[e] = __fmaf_rn(x[e], c, __fmul_rn(rotated, s));   // the reference's compiled form of x*cos + rot*sin: one product rounded, one fused
+    for (int e = 0; e < 4; ++e) r[e] = x[e];
+  } else {
+#pragma unroll
+    for (int e = 0; e < 4; ++e) {
+      const int d = 4 * lane + e, sd = d & 63;
+      const float other = __shfl_xor_sync(0xffffffffu, x[e], 16);   // channel d +- 64 lives 16 lanes away
+      const float rotated = lane < 16 ? -other : other;
+      const int axis = sd < a.section0 ? 0 : (sd < a.section0 + a.section1 ? 1 : 2);
+      const float c = load_rot(a.cos, axis * a.cos_stride[0] + request * a.cos_stride[1] + token * a.cos_stride[2] + d * a.cos_stride[3],
+                               a.rot_dtype);
+      const float s = load_rot(a.sin, axis * a.sin_stride[0] + request * a.sin_stride[1] + token * a.sin_stride[2] + d * a.sin_stride[3],
+                               a.rot_dtype);
+      r[e] = __fmaf_rn(x[e], c, __fmul_rn(rotated, s));   // the reference's compiled form of x*cos + rot*sin: one product rounded, one fused
+    }
   }
-  if (a.hadamard) {
+  if (which == 2 || a.hadamard) {
     const float p = __fadd_rn(r[0], r[1]), m = __fsub_rn(r[0], r[1]), c = __fadd_rn(r[2], r[3]), d = __fsub_rn(r[2], r[3]);
     r[0] = __fadd_rn(p, c); r[1] = __fadd_rn(m, d); r[2] = __fsub_rn(p, c); r[3] = __fsub_rn(m, d);
 #pragma unroll
@@ -399,7 +418,7 @@ __global__ void mrope_rows_kernel(MropeArgs a) {
     __half2 lo = __floats2half2_rn(r[0], r[1]), hi = __floats2half2_rn(r[2], r[3]);
     pk.x = *reinterpret_cast<uint32_t*>(&lo); pk.y = *reinterpret_cast<uint32_t*>(&hi);
   }
-  *reinterpret_cast<uint2*>((is_q ? a.q_out : a.k_out) + off + 4 * lane) = pk;
+  *reinterpret_cast<uint2*>(dst + off + 4 * lane) = pk;
 }
 
 }  // namespace r2k

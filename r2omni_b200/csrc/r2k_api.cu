@@ -730,7 +730,43 @@ int r2k_qk_mrope(const void* q, const void* k, void* q_out, void* k_out, int32_t
   for (int i = 0; i < 4; ++i) { a.cos_stride[i] = cos_strides[i]; a.sin_stride[i] = sin_strides[i]; }
   a.batch = batch; a.hq = num_q_heads; a.hkv = num_kv_heads; a.tokens = tokens;
   a.section0 = section0; a.section1 = section1; a.rot_dtype = rot_dtype; a.hadamard = apply_hadamard ? 1 : 0;
+  a.v = nullptr; a.v_out = nullptr; a.v_hadamard = 0; a.v_bstride = 0;
+  a.q_bstride = (int64_t)num_q_heads * tokens * 128; a.k_bstride = (int64_t)num_kv_heads * tokens * 128;
   const int64_t rows = (int64_t)batch * (num_q_heads + num_kv_heads) * tokens;
+  const unsigned grid = (unsigned)((rows + 3) / 4);
+  cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
+  if (dtype == R2K_DTYPE_BF16) mrope_rows_kernel<true><<<grid, 128, 0, st>>>(a);
+  else mrope_rows_kernel<false><<<grid, 128, 0, st>>>(a);
+  ++g_launches;
+  return cudaGetLastError() == cudaSuccess ? R2K_OK : R2K_ERR_CUDA;
+}
+
+int r2k_qkv_prologue(const void* q, int64_t q_bstride, const void* k, int64_t k_bstride, const void* v, int64_t v_bstride,
+                     void* q_out, void* k_out, void* v_out, int32_t dtype, int32_t batch, int32_t num_q_heads,
+                     int32_t num_kv_heads, const void* cos, const void* sin, int32_t rot_dtype, const int64_t cos_strides[4],
+                     const int64_t sin_strides[4], int32_t section0, int32_t section1, int32_t key_hadamard,
+                     int32_t value_hadamard, void* stream) {
+  if (!q || !k || !v || !q_out || !k_out || !v_out || !cos || !sin || !cos_strides || !sin_strides) return R2K_ERR_NULL;
+  if ((dtype != R2K_DTYPE_BF16 && dtype != R2K_DTYPE_FP16) || (rot_dtype != R2K_DTYPE_BF16 && rot_dtype != R2K_DTYPE_FP16 && rot_dtype != 2))
+    return R2K_ERR_GEOMETRY;
+  if (batch < 1 || num_q_heads < 1 || num_kv_heads < 1) return R2K_ERR_GEOMETRY;
+  if (section0 < 0 || section1 < 0 || section0 + section1 > 64) return R2K_ERR_GEOMETRY;
+  if (q_bstride < (int64_t)num_q_heads * 128 || k_bstride < (int64_t)num_kv_heads * 128 || v_bstride < (int64_t)num_kv_heads * 128)
+    return R2K_ERR_GEOMETRY;
+  if ((reinterpret_cast<uintptr_t>(q) | reinterpret_cast<uintptr_t>(k) | reinterpret_cast<uintptr_t>(v) |
+       reinterpret_cast<uintptr_t>(q_out) | reinterpret_cast<uintptr_t>(k_out) | reinterpret_cast<uintptr_t>(v_out)) & 7u)
+    return R2K_ERR_ALIGNMENT;
+  if ((q_bstride | k_bstride | v_bstride) & 3) return R2K_ERR_ALIGNMENT;   // 8-byte loads of four channels
+  MropeArgs a;
+  a.q = reinterpret_cast<const uint16_t*>(q); a.k = reinterpret_cast<const uint16_t*>(k); a.v = reinterpret_cast<const uint16_t*>(v);
+  a.q_out = reinterpret_cast<uint16_t*>(q_out); a.k_out = reinterpret_cast<uint16_t*>(k_out); a.v_out = reinterpret_cast<uint16_t*>(v_out);
+  a.q_bstride = q_bstride; a.k_bstride = k_bstride; a.v_bstride = v_bstride;
+  a.cos = cos; a.sin = sin;
+  for (int i = 0; i < 4; ++i) { a.cos_stride[i] = cos_strides[i]; a.sin_stride[i] = sin_strides[i]; }
+  a.batch = batch; a.hq = num_q_heads; a.hkv = num_kv_heads; a.tokens = 1;
+  a.section0 = section0; a.section1 = section1; a.rot_dtype = rot_dtype;
+  a.hadamard = key_hadamard ? 1 : 0; a.v_hadamard = value_hadamard ? 1 : 0;
+  const int64_t rows = (int64_t)batch * (num_q_heads + 2 * num_kv_heads);
   const unsigned grid = (unsigned)((rows + 3) / 4);
   cudaStream_t st = reinterpret_cast<cudaStream_t>(stream);
   if (dtype == R2K_DTYPE_BF16) mrope_rows_kernel<true><<<grid, 128, 0, st>>>(a);

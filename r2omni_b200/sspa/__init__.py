@@ -14,7 +14,7 @@ from .cache import (
     precision_cache_storage_breakdown,
 )
 from .dynamic import DynamicCacheStats, append_generated_token, flush_recent
-from .hadamard import normalized_fwht, qwen_qk_mrope, triton_fwht_128
+from .hadamard import normalized_fwht, qwen_qk_mrope, qwen_qkv_prologue, triton_fwht_128
 from .integration import KERNEL_BACKEND, LayerState, PackedKVAttentionManager
 from .sharded import SequenceShardedExecutor, shard_token_range
 from .executor import (
@@ -37,5 +37,5 @@ __all__ = [
     "SplitKExecutor", "SplitKWorkspace", "allocate_splitk_workspace", "allocated_workspace_bytes",
     "append_recent_fp", "append_recent_fp_triton", "prepare_splitk_executor", "required_splitk_blocks",
     "stack_homogeneous_splitk_executors", "SequenceShardedExecutor", "shard_token_range",
-    "triton_fwht_128", "normalized_fwht", "qwen_qk_mrope", "KERNEL_BACKEND", "LayerState", "PackedKVAttentionManager",
+    "triton_fwht_128", "normalized_fwht", "qwen_qk_mrope", "qwen_qkv_prologue", "KERNEL_BACKEND", "LayerState", "PackedKVAttentionManager",
 ]

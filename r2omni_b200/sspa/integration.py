@@ -25,7 +25,7 @@ from .cache import ThreePrecisionCache
 from .dynamic import DynamicCacheStats, append_generated_token, flush_recent
 from .executor import (SplitKExecutor, allocate_splitk_workspace, prepare_splitk_executor,
                        stack_homogeneous_splitk_executors)
-from .hadamard import qwen_qk_mrope, triton_fwht_128
+from .hadamard import qwen_qk_mrope, qwen_qkv_prologue, triton_fwht_128
 
 KERNEL_BACKEND = "cuda_sm100"
 
@@ -100,7 +100,9 @@ class PackedKVAttentionManager:
 
     # ---- one decode step -----------------------------------------------------------------------------------
     def _project_qkv(self, module: Any, hidden_states: torch.Tensor, position_embeddings):
-        """qwen_sspa_attention.py:1202-1248 (the Qwen2.5-Omni branch: fused multimodal RoPE, optional Hadamard)."""
+        """qwen_sspa_attention.py:1202-1248 (the Qwen2.5-Omni branch: fused multimodal RoPE, optional Hadamard).
+        Returns (q, k, v, value_ready): with a fused ``qkv_proj`` on the module the value rows come back already
+        rotated when ``value_hadamard`` is on."""
         batch_size = int(hidden_states.shape[0])
         if int(hidden_states.shape[1]) != 1:
             raise ValueError("compact fused mRoPE decode requires one token per request")
@@ -110,12 +112,21 @@ class PackedKVAttentionManager:
         if position_embeddings is None or len(position_embeddings) != 2:
             raise ValueError("Qwen position_embeddings are required")
         d = int(module.head_dim)
+        cos, sin = position_embeddings
+        fused = getattr(module, "qkv_proj", None)
+        if fused is not None:
+            # one projection for the three (not in the reference's modules; serving stacks fuse them): its output is
+            # read in place by the prologue launch, which also brings the value rows along, rotated when asked to
+            qkv = fused(hidden_states)
+            nq = self.num_query_heads * d
+            nkv = (int(qkv.shape[-1]) - nq) // 2
+            return qwen_qkv_prologue(qkv[..., :nq], qkv[..., nq : nq + nkv], qkv[..., nq + nkv :], cos, sin, self.mrope_section,
+                                     key_hadamard=self.key_hadamard, value_hadamard=self.value_hadamard) + (True,)
         q = module.q_proj(hidden_states).view(batch_size, 1, -1, d).transpose(1, 2).contiguous()
         k = module.k_proj(hidden_states).view(batch_size, 1, -1, d).transpose(1, 2).contiguous()
         v = module.v_proj(hidden_states).view(batch_size, 1, -1, d).transpose(1, 2).contiguous()
-        cos, sin = position_embeddings
         q, k = qwen_qk_mrope(q, k, cos, sin, self.mrope_section, apply_hadamard=self.key_hadamard)
-        return q, k, v
+        return q, k, v, False
 
     def _kernel_value(self, value: torch.Tensor) -> torch.Tensor:
         return triton_fwht_128(value) if self.value_hadamard else value
@@ -152,8 +163,8 @@ class PackedKVAttentionManager:
         (device i64 ``[B,2]``) instead."""
         state = self._states[int(layer_id)]
         state.calls += 1
-        q, new_k, new_v = self._project_qkv(module, hidden_states, position_embeddings)
-        kernel_new_k, kernel_new_v = new_k, self._kernel_value(new_v)
+        q, new_k, new_v, value_ready = self._project_qkv(module, hidden_states, position_embeddings)
+        kernel_new_k, kernel_new_v = new_k, (new_v if value_ready else self._kernel_value(new_v))
         current_position = state.original_seq_len if cache_position is None else int(cache_position)
         arenas = state.fourq_executor.arenas
         fused_append = None

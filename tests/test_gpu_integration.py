@@ -95,6 +95,45 @@ def test_manager_decode_steps_match_the_oracle_composition(batch, value_hadamard
     assert state.fourq_executor.device_status() == 0
 
 
+@pytest.mark.parametrize("value_hadamard", [False, True])
+def test_fused_projection_module_gives_the_same_steps(value_hadamard):
+    """A module with one ``qkv_proj`` (weights of the three projections stacked) goes through the one-launch
+    prologue; a twin manager with the three projections goes through the reference's sequence of calls.  Same
+    attention rows, bit for bit, step after step, through a flush."""
+    pages, page, batch = 12, 64, 2
+    seq = pages * page
+    classes = torch.tensor([1, 2, 5, 2, 2, 1, 5, 2, 1, 2, 5, 2])
+    managers = [R.PackedKVAttentionManager(num_query_heads=HQ, mrope_section=SECTIONS, value_hadamard=value_hadamard)
+                for _ in range(2)]
+    for m in managers:
+        caches = []
+        for b in range(batch):
+            key, value, _, _, _ = make_inputs(seed=60 + b, hq=HQ, hkv=HKV, tokens=seq, appends=1, n_queries=1)
+            caches.append(build_gpu_cache(key, value, classes, page_size=page, append_capacity=256))
+        m.adopt_layer(0, caches, seq)
+    split = _to(_module(7), "cuda")
+    qkv = torch.nn.Linear(HIDDEN, (HQ + 2 * HKV) * 128, bias=True, device="cuda", dtype=torch.bfloat16)
+    with torch.no_grad():
+        qkv.weight.copy_(torch.cat([split.q_proj.weight, split.k_proj.weight, split.v_proj.weight], 0))
+        qkv.bias.copy_(torch.cat([split.q_proj.bias, split.k_proj.bias, split.v_proj.bias], 0))
+    fused = SimpleNamespace(head_dim=128, qkv_proj=qkv, o_proj=split.o_proj)
+    g = torch.Generator().manual_seed(13)
+    for i in range(131):
+        hidden = torch.randn(batch, 1, HIDDEN, generator=g).to(torch.bfloat16).cuda()
+        cos, sin = _rotary(batch, float(i), g)
+        a = managers[0].active_forward(0, split, hidden, (cos.cuda(), sin.cuda()), cache_position=seq + i).clone()
+        rows_a = managers[0]._states[0].fourq_executor.workspace.output.clone()
+        b = managers[1].active_forward(0, fused, hidden, (cos.cuda(), sin.cuda()), cache_position=seq + i)
+        rows_b = managers[1]._states[0].fourq_executor.workspace.output
+        # one GEMM over the stacked weights and three GEMMs may round differently in the last bit of a projection;
+        # the attention tolerance covers what that does to the rows
+        assert_close(rows_b, rows_a, f"step {i}")
+        assert (a.float() - b.float()).abs().max().item() < 0.05
+    assert managers[1].get_stats()[0]["generated_recompress_count"] == 1
+    for m in managers:
+        assert m._states[0].fourq_executor.device_status() == 0
+
+
 def test_manager_rejects_what_the_reference_manager_rejects():
     manager = R.PackedKVAttentionManager(num_query_heads=HQ)
     key, value, _, _, _ = make_inputs(seed=95, hq=HQ, hkv=HKV, tokens=512, appends=1, n_queries=1)

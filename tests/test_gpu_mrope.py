@@ -64,3 +64,52 @@ def test_mrope_matches_the_reference_kernel_fixture():
         got_q, got_k = R.qwen_qk_mrope(q.cuda(), k.cuda(), cos.cuda(), sin.cuda(), SECTIONS, apply_hadamard=hadamard)
         assert np.array_equal(got_q.cpu().view(torch.int16).numpy(), z[name + "_q"]), name
         assert np.array_equal(got_k.cpu().view(torch.int16).numpy(), z[name + "_k"]), name
+
+
+@pytest.mark.parametrize("dtype,rot_dtype", [(torch.bfloat16, torch.bfloat16), (torch.bfloat16, torch.float32),
+                                             (torch.float16, torch.float16)])
+@pytest.mark.parametrize("batch,hq,hkv", [(1, 16, 2), (8, 16, 2), (3, 28, 4), (2, 3, 1)])
+@pytest.mark.parametrize("key_hadamard,value_hadamard", [(False, False), (True, False), (False, True), (True, True)])
+def test_one_launch_prologue_equals_the_separate_calls(dtype, rot_dtype, batch, hq, hkv, key_hadamard, value_hadamard):
+    """Query, key and value rows read in place from one fused projection output (rows 4 elements apart from where a
+    contiguous tensor would have them, to make sure the stride is used): the same bits as the rotation call on
+    contiguous copies and the Hadamard call on the value rows, and as the oracle."""
+    g = torch.Generator().manual_seed(1000 + batch * 37 + hq)
+    width = (hq + 2 * hkv) * 128
+    fused = torch.randn(batch, 1, width + 4, generator=g).to(dtype).cuda()[..., :width]
+    q, k, v = fused[..., : hq * 128], fused[..., hq * 128 : (hq + hkv) * 128], fused[..., (hq + hkv) * 128 :]
+    assert not q.is_contiguous() or batch == 1
+    _, _, cos, sin = _inputs(batch, hq, hkv, 1, dtype, rot_dtype, seed=batch + hq)
+    sections = (16, 24, 24)
+    cos, sin = cos.cuda(), sin.cuda()
+    got_q, got_k, got_v = R.qwen_qkv_prologue(q, k, v, cos, sin, sections, key_hadamard=key_hadamard,
+                                              value_hadamard=value_hadamard)
+    qc = q.reshape(batch, 1, hq, 128).transpose(1, 2).contiguous()
+    kc = k.reshape(batch, 1, hkv, 128).transpose(1, 2).contiguous()
+    vc = v.reshape(batch, 1, hkv, 128).transpose(1, 2).contiguous()
+    want_q, want_k = R.qwen_qk_mrope(qc, kc, cos, sin, sections, apply_hadamard=key_hadamard)
+    want_v = R.triton_fwht_128(vc) if value_hadamard else vc
+    for got, want in ((got_q, want_q), (got_k, want_k), (got_v, want_v)):
+        assert got.shape == want.shape and got.is_contiguous()
+        assert torch.equal(got.view(torch.int16), want.view(torch.int16))
+    oq, ok = O.qk_mrope(qc.cpu(), kc.cpu(), cos.cpu(), sin.cpu(), sections, key_hadamard)
+    assert torch.equal(got_q.cpu().view(torch.int16), oq.view(torch.int16))
+    assert torch.equal(got_k.cpu().view(torch.int16), ok.view(torch.int16))
+    if value_hadamard:
+        assert torch.equal(got_v.cpu().view(torch.int16), O.fwht128(vc.cpu().float()).to(dtype).view(torch.int16))
+
+
+def test_one_launch_prologue_rejects_bad_arguments():
+    fused = torch.randn(2, 1, 20 * 128).to(torch.bfloat16).cuda()
+    q, k, v = fused[..., :2048], fused[..., 2048:2304], fused[..., 2304:]
+    _, _, cos, sin = _inputs(2, 16, 2, 1, torch.bfloat16, torch.float32, seed=4)
+    cos, sin = cos.cuda(), sin.cuda()
+    R.qwen_qkv_prologue(q, k, v, cos, sin, (16, 24, 24))
+    with pytest.raises(ValueError):
+        R.qwen_qkv_prologue(q, k, v[..., :128], cos, sin, (16, 24, 24))          # key and value heads differ
+    with pytest.raises(ValueError):
+        R.qwen_qkv_prologue(q, k, v, cos[:, :1], sin[:, :1], (16, 24, 24))      # tables of another batch
+    with pytest.raises(ValueError):
+        R.qwen_qkv_prologue(q, k, v, cos, sin, (16, 24, 20))
+    with pytest.raises(RuntimeError):
+        R.qwen_qkv_prologue(q.cpu(), k.cpu(), v.cpu(), cos.cpu(), sin.cpu(), (16, 24, 24))
